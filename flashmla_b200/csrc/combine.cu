@@ -27,12 +27,15 @@ combine_kernel(int s_q, int h_q, const int* __restrict__ num_splits, const float
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int batch = blockIdx.x / s_q, sq = blockIdx.x % s_q;
   const int head = blockIdx.y * COMBINE_HEADS_PER_BLOCK + warp;
-  if (head >= h_q) return;
-  const int first = num_splits[batch], n = num_splits[batch + 1] - first;   // scheduler output: written long before
-  if (n <= 1) return;
   // The kernel may have been launched while the attention kernel was still running (programmatic dependent
-  // launch): its partial results are complete and visible only after this wait.
+  // launch): its partial results are complete and visible only after this wait.  Every thread runs it, also
+  // those that have nothing to merge: a grid whose blocks all left before the wait would complete ahead of the
+  // attention kernel, and the next kernel in the stream - ordered behind this grid only - could then read
+  // `out` / `lse` of unsplit requests while the attention kernel was still writing them.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (head >= h_q) return;
+  const int first = num_splits[batch], n = num_splits[batch + 1] - first;
+  if (n <= 1) return;
 
   const int64_t part_stride_lse = (int64_t)s_q * h_q;
   const int64_t part_stride_o = part_stride_lse * D_V;

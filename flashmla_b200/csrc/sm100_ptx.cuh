@@ -81,13 +81,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity)
   return false;
 }
 // Bounded wait that also gives up as soon as `*abort_flag` (shared memory) becomes non-zero, so that one
-// role's time-out releases every other role quickly.
+// role's time-out releases every other role quickly.  POLLS is the poll limit (the kernels use WAIT_POLLS).
+template <uint32_t POLLS = WAIT_POLLS>
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+  for (uint32_t i = 0; i < POLLS; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef FMLA_WAIT_SLEEP
-    __nanosleep(FMLA_WAIT_SLEEP);
-#endif
     if ((i & 63u) == 63u && *abort_flag != 0) return false;
   }
   return false;

@@ -79,6 +79,11 @@ constexpr uint32_t RAW_BYTES = (RAW_TAIL + (T / 4) * TAIL_GROUP + 1023) / 1024 *
 constexpr uint32_t RAW_TX_BYTES = T * (256 + TAIL_BYTES), STAGE_TX_BYTES = T * (512 + 64);
 constexpr uint32_t P_BYTES = 64 * 128;
 constexpr uint32_t TM_O = 0, TM_Q = 256, TM_S = 400, TM_COLS = 512;
+// Registers per thread after the warpgroups have re-divided the register file.  The pool is what the launch gave the
+// CTA (96 per thread, the most that 640 threads can have), not the SM's whole file: an increase beyond it never returns.
+constexpr int REGS_LAUNCH = 96, REGS_SOFTMAX = 128, REGS_PRODUCER = 80, REGS_ISSUER = 64;
+static_assert(NSW * REGS_SOFTMAX + NPW * REGS_PRODUCER + (2 + NGW) * REGS_ISSUER <= (NSW + NPW + 2 + NGW) * REGS_LAUNCH, "register pool");
+static_assert(NSW % 4 == 0 && NPW % 4 == 0 && (2 + NGW) % 4 == 0, "roles fill whole warpgroups");
 constexpr float RESCALE_THRESHOLD = 6.f;   // log2 units the block maximum may exceed the reference maximum
 constexpr int RING = 8;                    // slots of the index and validity-mask rings
 constexpr int IDX_LOOKAHEAD = 6;           // prefill: blocks the index prefetch runs ahead of the gathers
@@ -86,51 +91,28 @@ constexpr int IDX_LOOKAHEAD = 6;           // prefill: blocks the index prefetch
 // shared-memory map (offsets from a 1024-byte aligned base)
 enum Bar { KV_FULL = 0, KV_EMPTY = KV_FULL + MAX_STAGES,
            RAW_FULL = KV_EMPTY + MAX_STAGES /* [NGW][NRAW] */, RAW_EMPTY = RAW_FULL + NGW * NRAW /* [NGW][NRAW] */,
-           S_FULL = RAW_EMPTY + NGW * NRAW, S_EMPTY, P_FULL, PV_DONE = P_FULL + 2, Q_FULL = PV_DONE + 2, QT_FULL /* [2 feature halves] */, NUM_BARS = QT_FULL + 2 };
+           S_FULL = RAW_EMPTY + NGW * NRAW /* [2 teams] */, S_EMPTY = S_FULL + 2, P_FULL /* [2 teams] */, PV_DONE = P_FULL + 2 /* [2 teams] */,
+           DEC = PV_DONE + 2 /* [2 teams] */, Q_FULL = DEC + 2, QT_FULL /* [2 feature halves] */, NUM_BARS = QT_FULL + 2 };
 constexpr uint32_t SM_BAR = 0;
 constexpr uint32_t SM_TMEM = SM_BAR + NUM_BARS * 8;
 constexpr uint32_t SM_ABORT = SM_TMEM + 4;
 constexpr uint32_t SM_LEAVE = SM_ABORT + 4;                 // softmax warps that have left because of an abort
 constexpr uint32_t SM_MASK = 512;                           // uint8 [RING][8]: validity bits of the 8 tokens of producer warp w
-constexpr uint32_t SM_MAX = 1024;                           // float [2 block parities][4][64]
-constexpr uint32_t SM_SUM = SM_MAX + 2048;                  // float [4][64]
+constexpr uint32_t SM_MAX = 1024;                           // float [2 teams][2 halves][64]: block maxima of a thread's 32 tokens
+constexpr uint32_t SM_MREF = SM_MAX + 1024;                 // float [2 teams][64]: reference maximum after the team's latest block
+constexpr uint32_t SM_SUM = SM_MAX + 2048;                  // float [4][64]: row sums at the end of a query
 constexpr uint32_t SM_IDX = SM_SUM + 1024;                  // int32 [NPW producer warps][RING][PROWS]
-constexpr uint32_t SM_P = 6144;                             // two P buffers, 1024-byte aligned
-constexpr uint32_t SM_XCHG = SM_P + 2 * P_BYTES;            // float [2 column groups][2 halves][64 heads][16], chunk-swizzled
-constexpr uint32_t SM_STAGE = SM_XCHG + 2 * 32 * 64 * 4;    // stages, then (decode) the raw ring
+constexpr uint32_t SM_MTRUE = SM_IDX + NPW * RING * PROWS * 4;   // float [4][64]: largest logits at the end of a query
+constexpr uint32_t SM_P = 7168;                             // two P buffers (one per team), 1024-byte aligned
+constexpr uint32_t SM_XCHG = SM_P + 2 * P_BYTES;            // float [2 receiving halves][64 heads][32], chunk-swizzled; also the Q tiles
+constexpr uint32_t SM_STAGE = SM_XCHG + 2 * 64 * 32 * 4;    // stages, then (decode) the raw ring
 constexpr uint32_t SM_RAW = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
-static_assert(SM_LEAVE + 4 <= SM_MASK && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 && SM_STAGE % 1024 == 0 &&
+static_assert(SM_LEAVE + 4 <= SM_MASK && SM_MTRUE + 1024 <= SM_P && SM_P % 1024 == 0 && SM_STAGE % 1024 == 0 &&
               STAGE_BYTES % 1024 == 0 && SM_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0, "shared memory map");
 constexpr uint32_t SMEM_USED_PREFILL = SM_STAGE + NSTAGE_PREFILL * STAGE_BYTES;
 constexpr uint32_t SMEM_USED_DECODE = SM_RAW + NRAW * RAW_BYTES;
 constexpr uint32_t SMEM_BYTES = (SMEM_USED_PREFILL > SMEM_USED_DECODE ? SMEM_USED_PREFILL : SMEM_USED_DECODE) + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
-
-// Optional cycle accounting per role (compiled in with -DFMLA_PROFILE only): one thread per role adds
-// the cycles between consecutive marks to a slot and dumps its slots to g_prof[cta][64] at the end.
-#ifdef FMLA_PROFILE
-__device__ long long* g_prof = nullptr;
-struct Prof {
-  long long t, acc[16];
-  bool on;
-  __device__ Prof(bool enable) : on(enable) { for (int i = 0; i < 16; ++i) acc[i] = 0; t = clock64(); }
-  __device__ __forceinline__ void mark(int slot) { if (on) { const long long now = clock64(); acc[slot] += now - t; t = now; } }
-  __device__ __forceinline__ void count(int slot) { if (on) acc[slot] += 1; }
-  __device__ void dump(int base) {
-    if (on && g_prof) {
-      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-      for (int i = 0; i < 16; ++i) atomicAdd(reinterpret_cast<unsigned long long*>(g_prof + cta * 64 + base + i), (unsigned long long)acc[i]);
-    }
-  }
-};
-#else
-struct Prof {
-  __device__ Prof(bool) {}
-  __device__ __forceinline__ void mark(int) {}
-  __device__ __forceinline__ void count(int) {}
-  __device__ __forceinline__ void dump(int) {}
-};
-#endif
 
 struct Params {
   CUtensorMap map_nope, map_rope;   // decode: byte views of the pool (256-byte NoPE box, 144-byte tail box); prefill: bf16 views of kv
@@ -245,6 +227,9 @@ __device__ __forceinline__ bool get_item(const P& p, const SchedRecord& rec, int
 }
 
 __device__ __forceinline__ int num_blocks(const Item& it) { return (it.tok_hi - it.tok_lo + T - 1) / T; }
+
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // ---- abort plumbing ----------------------------------------------------------------------------
 struct Ctx {
@@ -376,7 +361,6 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
   const int range = p.s_kv;
   const uint32_t ring = c.base + SM_IDX + (uint32_t)pwarp * (RING * PROWS * 4);
   BlockCursor feed(p, rec), gat(p, rec);
-  Prof pf(ptid == 0);
 
   auto feed_block = [&](uint32_t blk) {       // indices of block blk -> ring slot blk % RING; one cp.async group
     if (feed.live) {
@@ -401,12 +385,10 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
     // groups 0 .. g+IDX_LOOKAHEAD-1 are committed; with at most IDX_LOOKAHEAD-1 pending, group g has landed
     cp_async_wait<IDX_LOOKAHEAD - 1>();
     __syncwarp();
-    pf.mark(1);
     const int st = g % nst;
     const uint32_t use = g / nst;
     bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 12);
     if (!__all_sync(0xffffffffu, ok)) return;
-    pf.mark(7);
     const uint32_t dst = stage_addr(c, st);
     const uint32_t bar = map_to_cta(bar_addr(c, KV_FULL + st), 0);      // shared::cluster address of the leader's stage barrier
     uint32_t bits = 0;
@@ -433,11 +415,9 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
       const int col = kind < 4 ? 256 * (int)rank + 64 * kind : 512 + 32 * (int)rank;
       tma_gather4_pair(map_to_cta(d, rank), map, col, make_int4(id[0], id[1], id[2], id[3]), bar);
     }
-    pf.mark(2);
     feed_block(g + IDX_LOOKAHEAD);
   }
   cp_async_wait<0>();
-  pf.dump(16);
 }
 
 // ---- decode: gather warps and converter warps -----------------------------------------------------------
@@ -451,7 +431,6 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
   const int q = lane >> 1, kind = lane & 1;
   const bool active = q < 8;
   BlockCursor ld(p, rec), gat(p, rec);
-  Prof pf(lane == 0 && gw == 0);
   // the four cache indices of this lane's group in the block the cursor points at (-1 beyond the item's range)
   auto load_idx = [&](const BlockCursor& cu, int (&id)[4]) {
 #pragma unroll
@@ -473,12 +452,10 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
     int id[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
     ld.advance(p, rec);
     load_idx(ld, nxt);                                   // in flight while this block's gathers are issued
-    pf.mark(1);
     const int slot = g % NRAW;
     const uint32_t use = g / NRAW;
     bool ok = use == 0 || wait(c, RAW_EMPTY + gw * NRAW + slot, use - 1, 12);
     if (!__all_sync(0xffffffffu, ok)) return;
-    pf.mark(7);
     // a block lies entirely in the main or in the extra part of the token list (the boundary is a block multiple)
     const bool extra = gat.it.tok_lo + gat.n * T >= gat.it.main_end;
     const int range = extra ? (int)p.total_rows2 : (int)p.total_rows;
@@ -503,9 +480,7 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
       const CUtensorMap* map = extra ? (kind == 0 ? &p.map_nope2 : &p.map_rope2) : (kind == 0 ? &p.map_nope : &p.map_rope);
       tma_gather4(d, map, kind == 0 ? 256 * (int)rank : 512, make_int4(id[0], id[1], id[2], id[3]), bar);
     }
-    pf.mark(2);
   }
-  pf.dump(16);
 }
 
 template <class P>
@@ -513,16 +488,13 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   const int ptid = threadIdx.x - 32 * NSW, pwarp = ptid >> 5, lane = ptid & 31;
   const int gw = pwarp / (NPW / NGW);
   BlockCursor cur(p, rec);
-  Prof pf(ptid == 0);
   for (uint32_t g = 0; cur.live; ++g, cur.advance(p, rec)) {
     const int st = g % NSTAGE_DECODE, slot = g % NRAW;
     bool ok = wait(c, RAW_FULL + gw * NRAW + slot, g / NRAW, 14);
     if (!__all_sync(0xffffffffu, ok)) return;
-    pf.mark(3);
     const uint32_t use = g / NSTAGE_DECODE;
     ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
     if (!__all_sync(0xffffffffu, ok)) return;
-    pf.mark(4);
     const uint32_t raw = raw_addr(c, slot), stage = stage_addr(c, st);
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
@@ -543,14 +515,12 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       st_shared16(panel + swz(row, 2 * (ch & 3)), lo);
       st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi);
     }
-    pf.mark(8);
 #pragma unroll
     for (int it = 0; it < PROWS / 8; ++it) {
       const int f = 32 * it + lane, r = f >> 2, ch = f & 3;
       const uint32_t row = (uint32_t)PROWS * pwarp + r;
       st_shared16(stage + ROPE_PANEL + row * 64u + ((ch ^ ((row >> 1) & 3u)) << 4), lds_16(raw + RAW_TAIL + (row >> 2) * TAIL_GROUP + (row & 3u) * TAIL_BYTES + 16u + 64u * rank + ch * 16u));
     }
-    pf.mark(9);
     // the dequantised rows (generic proxy) become visible to the MMAs, and this warp's reads of the raw slot
     // are ordered before the TMA writes of the slot's next use
     fence_async_smem();
@@ -559,9 +529,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       mbar_arrive(bar_addr(c, RAW_EMPTY + gw * NRAW + slot));
       arrive_leader(c, KV_FULL + st);
     }
-    pf.mark(6);
   }
-  pf.dump(16);   // slots disjoint from the gather role's
 }
 
 // ---- MMA issuers (one thread each, CTA 0) ---------------------------------------------------------
@@ -573,18 +541,13 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
   const int nst = num_stages(p);
   Item it;
   uint32_t seq = 0;
-  Prof pf(true);
   for (int i = 0; get_item(p, rec, i, it); ++i) {
-    pf.mark(4);
     if (!wait(c, Q_FULL, i, 21)) return;
-    pf.mark(1);
     const int nb = num_blocks(it);
     for (int n = 0; n < nb; ++n, ++seq) {
       const int s = seq % nst;
       if (!wait(c, KV_FULL + s, seq / nst, 22)) return;
-      pf.mark(2);
       if (seq > 0 && !wait(c, S_EMPTY, seq - 1, 23)) return;
-      pf.mark(3);
       tc_fence_after_sync();
       const uint64_t b0 = smem_desc_kmajor(stage_addr(c, s));
       const uint64_t r0 = smem_desc_kmajor_sw64(stage_addr(c, s) + ROPE_PANEL);
@@ -593,11 +556,9 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
         const uint64_t bd = j < 16 ? b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4) : r0 + (((j - 16) * 32) >> 4);
         umma_ts<2>(tmem + TM_S, tmem + TM_Q + 8 * j, bd, j < 16 ? idesc_nope : idesc_rope, j > 0);
       }
-      umma_commit<2>(bar_addr(c, S_FULL), 0x3);
-      pf.mark(4);
+      umma_commit<2>(bar_addr(c, S_FULL + (seq & 1)), 0x3);
     }
   }
-  pf.dump(32);
 }
 
 template <class P>
@@ -606,15 +567,12 @@ __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint3
   const int nst = num_stages(p);
   Item it;
   uint32_t seq = 0;
-  Prof pf(true);
   for (int i = 0; get_item(p, rec, i, it); ++i) {
     const int nb = num_blocks(it);
     for (int n = 0; n < nb; ++n, ++seq) {
       const int s = seq % nst, b = seq & 1;
       if (!wait(c, P_FULL + b, seq >> 1, 31)) return;
-      pf.mark(1);
       if (!wait(c, KV_FULL + s, seq / nst, 32)) return;
-      pf.mark(2);
       tc_fence_after_sync();
       const uint64_t a0 = smem_desc_kmajor(c.base + SM_P + b * P_BYTES);
       const uint64_t v0 = smem_desc_mnmajor(stage_addr(c, s), PANEL);
@@ -626,10 +584,8 @@ __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint3
                      n > 0 || ks > 0);
       umma_commit<2>(bar_addr(c, KV_EMPTY + s), 0x3);
       umma_commit<2>(bar_addr(c, PV_DONE + b), 0x3);
-      pf.mark(3);
     }
   }
-  pf.dump(48);
 }
 
 
@@ -798,31 +754,32 @@ template <class P>
 __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem, uint32_t rank) {
   const int l = threadIdx.x;                 // 0..255
   const int warp = l >> 5, lane = l & 31;
-  const int L = l & 127, g = l >> 7;         // tensor-memory lane, column group
+  const int L = l & 127, team = l >> 7;      // tensor-memory lane, softmax team
   const int h = L & 63, half = L >> 6;
-  const int slot = 2 * g + half;             // this thread's place among the four threads of head h
+  const int g = team;                        // column group of this thread in the Q load and the epilogue
+  const int slot = 2 * team + half;          // this thread's place among the four threads of head h
   const int head = blockIdx.z * 128 + (int)rank * 64 + h;
   const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-  // of its 32 tokens a thread keeps 16 (the first 16 for half 0, the last 16 for half 1) and sends the rest to its partner
-  // region (g, receiving half) of the exchange buffer holds 64 rows (heads) of 16 floats; the 16-byte chunk k of
-  // row h sits at chunk position k ^ ((h >> 1) & 3), which spreads eight consecutive rows over all bank groups
-  const uint32_t xchg_put = c.base + SM_XCHG + 4096u * (2 * g + (1 - half)) + 64u * h;
-  const uint32_t xchg_get = c.base + SM_XCHG + 4096u * (2 * g + half) + 64u * h;
-  const uint32_t xsw = (uint32_t)(h >> 1) & 3u;
-  const uint32_t max_base = c.base + SM_MAX + 4u * h, sum_base = c.base + SM_SUM + 4u * h;
+  // Exchange buffer: region r (the receiving feature half) holds 64 rows (heads) of 32 floats; the 16-byte chunk k
+  // of row h sits at chunk position k ^ (h & 7), which spreads eight consecutive rows over all bank groups.
+  const uint32_t xchg_put = c.base + SM_XCHG + 8192u * (1 - half) + 128u * h;
+  const uint32_t xchg_get = c.base + SM_XCHG + 8192u * half + 128u * h;
+  const uint32_t xsw = (uint32_t)h & 7u;
+  const uint32_t max_mine = c.base + SM_MAX + 4u * (64 * slot + h), max_mate = c.base + SM_MAX + 4u * (64 * (slot ^ 1) + h);
+  const uint32_t mref_mine = c.base + SM_MREF + 4u * (64 * team + h), mref_other = c.base + SM_MREF + 4u * (64 * (team ^ 1) + h);
+  const uint32_t sum_base = c.base + SM_SUM + 4u * h, mtrue_base = c.base + SM_MTRUE + 4u * h;
   const bool real_head = head < p.h_q;     // h_q = 64 (mod 128): the last group's upper 64 heads are padding (Q = 0, nothing stored)
   const float sink2 = p.attn_sink && real_head ? __ldg(p.attn_sink + head) * LOG2E : -CUDART_INF_F;
+  const uint32_t leave_word = c.base + SM_LEAVE;
 
   Item it, it_next;
-  uint32_t seq = 0;
-  Prof pf(l == 0);
   bool have = get_item(p, rec, 0, it);
   const int head0 = blockIdx.z * 128 + (int)rank * 64;
   const bool q_issuer = h == 0 && g == 0;
   uint32_t qt_uses = 0;
   if (have) {
     if (p.q_tma) {
-      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, [] { return true; }, [](int) {})) { leave_group(c.base + SM_LEAVE, warp); return; }
+      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
     } else {
       load_q_to_tmem(p, it, tmem_lane, head, half, g);
     }
@@ -830,142 +787,138 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     __syncwarp();
     if (lane == 0) arrive_leader(c, Q_FULL);
   }
-  pf.mark(9);
+  uint32_t seq0 = 0;                         // number of blocks of the items before this one
   for (int i = 0; have; ++i) {
     const bool have_next = get_item(p, rec, i + 1, it_next);
     if (have_next) prefetch_q(p, it_next, head, half, g);
-    float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, l_sum = 0.f;
-    const int nb = num_blocks(it);
-    for (int n = 0; n < nb; ++n, ++seq) {
-      const int b = seq & 1;
-      bool ok = wait(c, S_FULL, seq, 41);
-      if (!__all_sync(0xffffffffu, ok)) { leave_group(c.base + SM_LEAVE, warp); return; }
-      pf.mark(1);
-      pf.count(11);
+    // m_mine: the reference maximum that l_sum is relative to; m_true: largest logit (base 2) of this team's blocks
+    float m_mine = -CUDART_INF_F, m_true = -CUDART_INF_F, l_sum = 0.f;
+    const uint32_t seq_end = seq0 + (uint32_t)num_blocks(it);
+    for (uint32_t seq = seq0 + ((seq0 ^ (uint32_t)team) & 1u); seq < seq_end; seq += 2) {
+      bool ok = wait(c, S_FULL + team, seq >> 1, 41);
+      // the other team has finished with the exchange buffer and has settled the reference maximum of block seq - 1
+      ok = ok && (seq == 0 || wait(c, DEC + (team ^ 1), (seq - 1) >> 1, 42));
+      if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
       tc_fence_after_sync();
-      // of the column group's 32 tokens this thread finishes 16 (tokens 32g+16half ..): it reads its own partial
-      // dot products of those ("keep") and of the other 16 ("send"), which go to its partner
-      uint32_t keep[16], send[16];
-      tmem_ld16(tmem_lane + TM_S + 32 * g + 16 * half, keep);
-      tmem_ld16(tmem_lane + TM_S + 32 * g + 16 * (1 - half), send);
+      // of the block's 64 tokens this thread finishes 32 (tokens 32*half ..): it reads its own partial dot
+      // products of the other 32 ("send"), which go to its mate in the other feature half, and of its own ("keep")
+      uint32_t keep[32];
+      {
+        uint32_t send[32];
+        tmem_ld32(tmem_lane + TM_S + 32 * (1 - half), send);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          st_shared16(xchg_put + (((uint32_t)k ^ xsw) << 4), make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
+      }
+      tmem_ld32(tmem_lane + TM_S + 32 * half, keep);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(c, S_EMPTY);
-      pf.mark(2);
-
-      // exchange partial dot products with the partner of the other feature half; x stays unscaled
-      float x[16];
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        st_shared16(xchg_put + ((k ^ xsw) << 4), make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
       pair_sync(warp);
+      float x[32];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint4 t = lds_16(xchg_get + ((k ^ xsw) << 4));
+      for (int k = 0; k < 8; ++k) {
+        const uint4 t = lds_16(xchg_get + (((uint32_t)k ^ xsw) << 4));
         x[4 * k] = __uint_as_float(keep[4 * k]) + __uint_as_float(t.x);
         x[4 * k + 1] = __uint_as_float(keep[4 * k + 1]) + __uint_as_float(t.y);
         x[4 * k + 2] = __uint_as_float(keep[4 * k + 2]) + __uint_as_float(t.z);
         x[4 * k + 3] = __uint_as_float(keep[4 * k + 3]) + __uint_as_float(t.w);
       }
-      pf.mark(3);
-      uint32_t vmask;
-      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(vmask) : "r"(c.base + SM_MASK + 8u * (seq % RING) + 2u * slot));
+      const uint32_t vmask = lds_u32(c.base + SM_MASK + 8u * (seq % RING) + 4u * half);
       float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < 32; ++j) {
         x[j] = (vmask >> j) & 1u ? x[j] : -CUDART_INF_F;
         mx = fmaxf(mx, x[j]);
       }
       mx *= p.scale_log2;                                  // the scale is positive: max commutes with it
-      const uint32_t mrow = max_base + 1024u * b;        // double-buffered by block parity
-      sts_f32(mrow + 256u * slot, mx);
-      // Prefill computes the exponentials against the current reference maximum while the row maxima travel
-      // between the four threads of the head; they stand unless the reference has to move (rare after the first
-      // blocks), in which case they are computed again (measured: 1 % faster in prefill, 1 % slower in decode, which
-      // therefore computes them after the exchange).  p = 2^(x * scale - m_ref); while no valid token has been
-      // seen every x is -inf and the offset is 0, so p = 0.
-      constexpr bool speculate = p.mode == 1;
-      uint32_t pk[8];
-      float sum = 0.f;
-      auto exponentials = [&](float off) {
-        sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float p0 = exp2f(fmaf(x[2 * j], p.scale_log2, off));
-          const float p1 = exp2f(fmaf(x[2 * j + 1], p.scale_log2, off));
-          sum += p0 + p1;
-          pk[j] = p.mode == 0 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
-        }
-      };
-      if (speculate) exponentials(m_ref == -CUDART_INF_F ? 0.f : -m_ref);
-      quad_sync(warp);
-      mx = fmaxf(fmaxf(mx, lds_f32(mrow + 256u * (slot ^ 1))), fmaxf(lds_f32(mrow + 256u * (slot ^ 2)), lds_f32(mrow + 256u * (slot ^ 3))));
+      sts_f32(max_mine, mx);
+      pair_sync(warp);
+      mx = fmaxf(mx, lds_f32(max_mate));                   // maximum of the block's 64 tokens for this head
       m_true = fmaxf(m_true, mx);
-      pf.mark(4);
 
-      // lazily move the reference maximum; the four threads of a head take the same decision
-      const bool bump = mx > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && mx != -CUDART_INF_F);
-      float alpha = 1.f;
-      if (bump) {
-        alpha = m_ref == -CUDART_INF_F ? 0.f : exp2f(m_ref - mx);
-        m_ref = mx;
-        l_sum *= alpha;
-        if (speculate) exponentials(-m_ref);
-      }
-      if (n > 0 && __any_sync(0xffffffffu, bump && alpha != 0.f)) {
-        ok = wait(c, PV_DONE + ((seq - 1) & 1), (seq - 1) >> 1, 44);
-        if (!__all_sync(0xffffffffu, ok)) { leave_group(c.base + SM_LEAVE, warp); return; }
+      // The reference maximum moves lazily: only when the block maximum exceeds it by more than the threshold.  The
+      // two teams take turns, so the value before this block is the one the other team left after block seq - 1
+      // (-inf at the first block of a query); the two threads of a head in this team take the same decision.
+      const float m_prev = seq == seq0 ? -CUDART_INF_F : lds_f32(mref_other);
+      const bool bump = mx > m_prev + RESCALE_THRESHOLD || (m_prev == -CUDART_INF_F && mx != -CUDART_INF_F);
+      const float m_new = bump ? mx : m_prev;
+      const float alpha = !bump ? 1.f : (m_prev == -CUDART_INF_F ? 0.f : exp2f(m_prev - mx));
+      if (half == 0) sts_f32(mref_mine, m_new);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_addr(c, DEC + team));
+      if (__any_sync(0xffffffffu, bump && alpha != 0.f)) {   // rescale this lane's 256 columns of O
+        // every PV product issued so far must have completed; this team's previous one first, so that the
+        // parity of the other team's barrier cannot be mistaken for the completion before
+        ok = seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 43);
+        ok = ok && wait(c, PV_DONE + (team ^ 1), (seq - 1) >> 1, 44);
+        if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 8; ++ch) {
           uint32_t o[32];
-          tmem_ld32(tmem_lane + TM_O + 128 * g + 32 * ch, o);
+          tmem_ld32(tmem_lane + TM_O + 32 * ch, o);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_st32(tmem_lane + TM_O + 128 * g + 32 * ch, o);
+          tmem_st32(tmem_lane + TM_O + 32 * ch, o);
         }
         tmem_st_wait();
-        pf.count(12);
       }
-      pf.mark(5);
-      if (!speculate) exponentials(m_ref == -CUDART_INF_F ? 0.f : -m_ref);
-      l_sum += sum;
-      pf.mark(6);
+      if (m_new != m_mine) { l_sum *= exp2f(m_mine - m_new); m_mine = m_new; }   // m_mine = -inf: l_sum is 0 and stays 0
 
-      if (seq >= 2) {
-        ok = wait(c, PV_DONE + b, (seq >> 1) - 1, 45);
-        if (!__all_sync(0xffffffffu, ok)) { leave_group(c.base + SM_LEAVE, warp); return; }
-      }
-      pf.mark(7);
-      const uint32_t pbuf = c.base + SM_P + b * P_BYTES;
+      // p = 2^(x * scale - m_ref); while no valid token has been seen every x is -inf and the offset is 0, so p = 0
+      const float off = m_new == -CUDART_INF_F ? 0.f : -m_new;
+      uint32_t pk[16];
+      float sum = 0.f;
 #pragma unroll
-      for (int k = 0; k < 2; ++k)
-        st_shared16(pbuf + swz(h, 2 * slot + k), make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]));
+      for (int j = 0; j < 16; ++j) {
+        const float p0 = exp2f(fmaf(x[2 * j], p.scale_log2, off));
+        const float p1 = exp2f(fmaf(x[2 * j + 1], p.scale_log2, off));
+        sum += p0 + p1;
+        pk[j] = p.mode == 0 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+      }
+      l_sum += sum;
+
+      if (seq >= 2) {                                      // the PV product that read this team's P buffer last
+        ok = wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
+        if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
+      }
+      const uint32_t pbuf = c.base + SM_P + team * P_BYTES;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        st_shared16(pbuf + swz(h, 4 * half + k), make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]));
       fence_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) arrive_leader(c, P_FULL + b);
-      pf.mark(8);
+      if (lane == 0) arrive_leader(c, P_FULL + team);
     }
+    seq0 = seq_end;
+    const uint32_t last = seq_end - 1;        // the query's last block
 
     // ---- end of the item: epilogue (columns 128g .. 128g+127 of the lane's 256) and the next query's Q ----
-    float mul = 0.f, lse2 = 0.f;
+    float mul = 0.f, lse2 = 0.f, m_fin = 0.f;
     bool empty = true;
     float* dst_f32 = nullptr;
     __nv_bfloat16* dst_bf16 = nullptr;
-    auto epi_begin = [&]() -> bool {            // row sums of the quad, output scale, destination
-      sts_f32(sum_base + 256u * slot, l_sum);
-      bool ok = wait(c, PV_DONE + ((seq - 1) & 1), (seq - 1) >> 1, 47);
+    // Runs after a barrier of all softmax warps: every S of this query has been consumed, so all its QK^T products
+    // are complete, and both teams have stored their last reference maximum.
+    auto epi_begin = [&]() -> bool {            // row sums and maxima of the quad, output scale, destination
+      m_fin = lds_f32(c.base + SM_MREF + 4u * (64 * (last & 1u) + h));
+      sts_f32(sum_base + 256u * slot, m_mine == m_fin ? l_sum : l_sum * exp2f(m_mine - m_fin));
+      sts_f32(mtrue_base + 256u * slot, m_true);
+      bool ok = wait(c, PV_DONE + (last & 1), last >> 1, 47);
       if (!__all_sync(0xffffffffu, ok)) return false;
       tc_fence_after_sync();
       quad_sync(warp);
-      const float l_tot = (l_sum + lds_f32(sum_base + 256u * (slot ^ 1))) + (lds_f32(sum_base + 256u * (slot ^ 2)) + lds_f32(sum_base + 256u * (slot ^ 3)));
+      const float l_tot = (lds_f32(sum_base) + lds_f32(sum_base + 256u)) + (lds_f32(sum_base + 512u) + lds_f32(sum_base + 768u));
+      m_true = fmaxf(fmaxf(lds_f32(mtrue_base), lds_f32(mtrue_base + 256u)), fmaxf(lds_f32(mtrue_base + 512u), lds_f32(mtrue_base + 768u)));
       empty = l_tot == 0.f;
-      lse2 = empty ? -CUDART_INF_F : m_ref + log2f(l_tot);
+      lse2 = empty ? -CUDART_INF_F : m_fin + log2f(l_tot);
       if (it.split) mul = empty ? 0.f : 1.f / l_tot;
-      else mul = empty ? 0.f : 1.f / (l_tot + exp2f(sink2 - m_ref));
+      else mul = empty ? 0.f : 1.f / (l_tot + exp2f(sink2 - m_fin));
       const int col0 = 256 * half + 128 * g;
       if (it.split) dst_f32 = p.o_accum + (it.row + head) * D_V + col0;
       else if (p.mode == 0) dst_bf16 = p.out + it.req * p.o_stride0 + it.sq * p.o_stride1 + head * p.o_stride_h + col0;
@@ -1005,34 +958,30 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         p.max_logits[it.row * p.h_q + head] = empty ? -CUDART_INF_F : m_true * LN2;
       }
     };
-    // Every QK^T of this item has completed (its last S was consumed above), so the next query's Q may replace it.
     // With the TMA path the epilogue's four chunks run between the Q tiles, in the shadow of their latency;
     // either way the next item's first QK^T overlaps the rest of the epilogue.
     if (have_next && p.q_tma) {
-      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, epi_begin, epi_chunk)) { leave_group(c.base + SM_LEAVE, warp); return; }
+      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(c, Q_FULL);
-      pf.mark(9);
     } else {
+      asm volatile("bar.sync 9, 256;" ::: "memory");
       if (have_next) {
         load_q_to_tmem(p, it_next, tmem_lane, head, half, g);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) arrive_leader(c, Q_FULL);
       }
-      pf.mark(9);
-      if (!epi_begin()) { leave_group(c.base + SM_LEAVE, warp); return; }
+      if (!epi_begin()) { leave_group(leave_word, warp); return; }
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) epi_chunk(ch);
     }
     epi_end();
     tc_fence_before_sync();
-    pf.mark(10);
     it = it_next;
     have = have_next;
   }
-  pf.dump(0);
 }
 
 // ---- kernel ------------------------------------------------------------------------------------------
@@ -1067,9 +1016,13 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
       mbar_init(bar_addr(c, RAW_FULL + s), 1);               // the gather warp's expect_tx arrival + the bytes
       mbar_init(bar_addr(c, RAW_EMPTY + s), NPW / NGW);      // the converter warps that read this half of the slot
     }
-    mbar_init(bar_addr(c, S_FULL), 1);
-    mbar_init(bar_addr(c, S_EMPTY), 2 * NSW);            // the softmax warps of both CTAs
-    for (int b = 0; b < 2; ++b) { mbar_init(bar_addr(c, P_FULL + b), 2 * NSW); mbar_init(bar_addr(c, PV_DONE + b), 1); }
+    mbar_init(bar_addr(c, S_EMPTY), NSW);                // the warps of one softmax team in both CTAs
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_addr(c, S_FULL + b), 1);
+      mbar_init(bar_addr(c, P_FULL + b), NSW);
+      mbar_init(bar_addr(c, PV_DONE + b), 1);
+      mbar_init(bar_addr(c, DEC + b), NSW / 2);          // the warps of one team of this CTA
+    }
     mbar_init(bar_addr(c, Q_FULL), 2 * NSW);
     for (int hf = 0; hf < 2; ++hf) mbar_init(bar_addr(c, QT_FULL + hf), 1);
     mbar_init_fence();
@@ -1082,18 +1035,25 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(c.base + SM_TMEM));
 
+  // The register file is re-divided between the warpgroups (four consecutive warps each): the softmax teams hold a
+  // block's 64 partial sums and 32 probabilities per thread, the other roles need few registers.
   if (warp < NSW) {
+    reg_inc<REGS_SOFTMAX>();
     softmax_role(p, rec, c, tmem, rank);
   } else if (warp < NSW + NPW) {
+    reg_dec<REGS_PRODUCER>();
     if (p.mode == 0) convert_role(p, rec, c, rank);
     else producer_role(p, rec, c, rank);
-  } else if (warp < GATHER_WARP) {
-    if (rank == 0 && (threadIdx.x & 31) == 0) {
-      if (warp == QK_WARP) issue_qk(p, rec, c, tmem);
-      else issue_pv(p, rec, c, tmem);
+  } else {
+    reg_dec<REGS_ISSUER>();
+    if (warp < GATHER_WARP) {
+      if (rank == 0 && (threadIdx.x & 31) == 0) {
+        if (warp == QK_WARP) issue_qk(p, rec, c, tmem);
+        else issue_pv(p, rec, c, tmem);
+      }
+    } else if (p.mode == 0) {
+      gather_role(p, rec, c, rank, warp - GATHER_WARP);
     }
-  } else if (p.mode == 0) {
-    gather_role(p, rec, c, rank, warp - GATHER_WARP);
   }
 
   tc_fence_before_sync();
@@ -1170,11 +1130,6 @@ static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
 
 }  // namespace tc
 
-#ifdef FMLA_PROFILE
-extern "C" int fmla_debug_set_profile_buffer(long long* buf) {
-  return cudaMemcpyToSymbol(tc::g_prof, &buf, sizeof(buf)) == cudaSuccess ? 0 : 4;
-}
-#endif
 
 bool tc_supported(int h_q) { return h_q > 0 && h_q % 64 == 0; }   // 64 (mod 128): the last pair runs half empty
 
