@@ -154,7 +154,11 @@ int fmla_sparse_decode(const FmlaDecodeArgs* a, void* cuda_stream) {
   DeviceGuard guard(a->device);
   FMLA_REQUIRE(guard.ok, FMLA_ERR_CUDA, "sparse_decode: cannot switch to device %d", a->device);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  int rc = k == FMLA_KERNEL_TC ? launch_tc_decode(*a, stream) : launch_simt_decode(*a, stream);
+  // AUTO: the tensor-core kernel when the head count, the cache strides and the scale allow it, else the generic one
+  // (which works with any partition count, so a plan made for the other kernel stays valid); an explicit
+  // FMLA_KERNEL_TC keeps the hard error.
+  const bool use_tc = k == FMLA_KERNEL_TC && (a->kernel == FMLA_KERNEL_TC || tc_decode_supported(*a));
+  int rc = use_tc ? launch_tc_decode(*a, stream) : launch_simt_decode(*a, stream);
   if (rc) return rc;
   if (a->attn_done_event) FMLA_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a->attn_done_event), stream));
   return launch_combine(*a, stream);
@@ -178,7 +182,8 @@ int fmla_sparse_prefill_fwd(const FmlaPrefillArgs* a, void* cuda_stream) {
   DeviceGuard guard(a->device);
   FMLA_REQUIRE(guard.ok, FMLA_ERR_CUDA, "sparse_prefill_fwd: cannot switch to device %d", a->device);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  return k == FMLA_KERNEL_TC ? launch_tc_prefill_fwd(*a, stream) : launch_simt_prefill_fwd(*a, stream);
+  const bool use_tc = k == FMLA_KERNEL_TC && (a->kernel == FMLA_KERNEL_TC || a->sm_scale > 0.f);   // AUTO: see fmla_sparse_decode
+  return use_tc ? launch_tc_prefill_fwd(*a, stream) : launch_simt_prefill_fwd(*a, stream);
 }
 
 int fmla_sparse_prefill_bwd(const FmlaPrefillBwdArgs* a, void* cuda_stream) {

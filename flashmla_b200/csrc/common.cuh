@@ -77,6 +77,7 @@ int launch_simt_prefill_bwd(const FmlaPrefillBwdArgs& a, cudaStream_t stream);
 // tensor-core (tcgen05) kernels
 bool tc_supported(int h_q);
 int tc_decode_plan(int num_sms, int h_q, int s_q, int* num_sm_parts, int* fixed_overhead_blocks, int* block_topk);
+bool tc_decode_supported(const FmlaDecodeArgs& a);      // stride and scale preconditions of the tensor-core decode kernel
 int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream);
 int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream);
 bool tc_bwd_supported(int h_q);

@@ -243,6 +243,17 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem] for a CTA pair, leaving some accumulator lanes untouched: bit i of lanes_off[j] set
+// means that tensor-memory lane 32 j + i keeps its value, j = 0..3 for CTA 0's lanes and 4..7 for CTA 1's.
+__device__ __forceinline__ void umma_ss_pair_masked(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate,
+                                                    const uint32_t (&lanes_off)[8]) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5,%6,%7,%8,%9,%10,%11,%12}, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(lanes_off[0]), "r"(lanes_off[1]), "r"(lanes_off[2]),
+                 "r"(lanes_off[3]), "r"(lanes_off[4]), "r"(lanes_off[5]), "r"(lanes_off[6]), "r"(lanes_off[7]) : "memory");
+}
+
 // Makes `bar` (in every CTA of cta_mask) receive one arrival when all MMAs issued so far by this
 // thread have completed.  `bar` is a shared::cta address valid at the same offset in each CTA.
 template <int CG>

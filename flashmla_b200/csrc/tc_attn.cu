@@ -63,69 +63,66 @@ using namespace ptx;
 constexpr int T = 64;                 // index slots per block
 constexpr int NPW = 8;                // producer warps per CTA
 constexpr int PROWS = 64 / NPW;       // tokens of a block owned by one producer warp
-constexpr int NSW = 8;                // softmax warps per CTA: two per quarter of the tensor-memory lanes
-constexpr int QK_WARP = NSW + NPW, PV_WARP = QK_WARP + 1;
-constexpr int NGW = 2;                // decode: gather warps, each fetching 32 of a block's 64 rows
-constexpr int GATHER_WARP = PV_WARP + 1;
-constexpr int THREADS = 32 * (GATHER_WARP + NGW);   // warps: NSW softmax, NPW producers, QK and PV issuers, NGW gather (decode)
-constexpr int NSTAGE_DECODE = 3, NSTAGE_PREFILL = 5, NRAW = 3, MAX_STAGES = 5;
+constexpr int NSW = 8;                // softmax warps per CTA: two teams of four (one warp per quarter of the tensor-memory lanes)
+// warps: NSW softmax, NPW producers / converters, two QK^T issuers (one per S buffer), the PV issuer, one idle warp
+constexpr int QK_WARP = NSW + NPW, PV_WARP = QK_WARP + 2, GATHER_WARP = PV_WARP + 1;
+constexpr int THREADS = 32 * (GATHER_WARP + 1);   // the last warp only fills the issuers' warpgroup
+constexpr int NSTAGE_DECODE = 5, NSTAGE_PREFILL = 5, MAX_STAGES = 5;
 constexpr uint32_t PANEL = T * 128;                 // one 128B-swizzled [64 tokens x 64 dims] panel
 constexpr uint32_t ROPE_PANEL = 4 * PANEL;          // offset of the 64B-swizzled [64 x 32] RoPE panel in a stage
 constexpr uint32_t STAGE_BYTES = 4 * PANEL + T * 64;
-// raw slot (decode): 64 rows x 256 NoPE bytes, then per group of four rows 4 x 144 "tail" bytes (the row's bytes
-// 512..655: scale field + both RoPE halves) padded to 640 so that every gather destination is 128-byte aligned
-constexpr uint32_t RAW_NOPE = 0, RAW_TAIL = T * 256, TAIL_BYTES = 144, TAIL_GROUP = 640;
-constexpr uint32_t RAW_BYTES = (RAW_TAIL + (T / 4) * TAIL_GROUP + 1023) / 1024 * 1024;
-constexpr uint32_t RAW_TX_BYTES = T * (256 + TAIL_BYTES), STAGE_TX_BYTES = T * (512 + 64);
+constexpr uint32_t STAGE_TX_BYTES = T * (512 + 64);
 constexpr uint32_t P_BYTES = 64 * 128;
-constexpr uint32_t TM_O = 0, TM_Q = 256, TM_S = 400, TM_COLS = 512;
+constexpr uint32_t QROPE_BYTES = 64 * 128;          // Q's RoPE part of this CTA's 64 heads: one 128B-swizzled [64 x 64] panel
+// tensor memory: O | Q (NoPE half of the lane: 256 dims, two per column) | two S buffers
+constexpr uint32_t TM_O = 0, TM_Q = 256, TM_S = 384, TM_COLS = 512;
 // Registers per thread after the warpgroups have re-divided the register file.  The pool is what the launch gave the
 // CTA (96 per thread, the most that 640 threads can have), not the SM's whole file: an increase beyond it never returns.
 constexpr int REGS_LAUNCH = 96, REGS_SOFTMAX = 128, REGS_PRODUCER = 80, REGS_ISSUER = 64;
-static_assert(NSW * REGS_SOFTMAX + NPW * REGS_PRODUCER + (2 + NGW) * REGS_ISSUER <= (NSW + NPW + 2 + NGW) * REGS_LAUNCH, "register pool");
-static_assert(NSW % 4 == 0 && NPW % 4 == 0 && (2 + NGW) % 4 == 0, "roles fill whole warpgroups");
+static_assert(NSW * REGS_SOFTMAX + NPW * REGS_PRODUCER + 4 * REGS_ISSUER <= (NSW + NPW + 4) * REGS_LAUNCH, "register pool");
+static_assert(NSW % 4 == 0 && NPW % 4 == 0 && THREADS == 32 * (NSW + NPW + 4), "roles fill whole warpgroups");
 constexpr float RESCALE_THRESHOLD = 6.f;   // log2 units the block maximum may exceed the reference maximum
 constexpr int RING = 8;                    // slots of the index and validity-mask rings
 constexpr int IDX_LOOKAHEAD = 6;           // prefill: blocks the index prefetch runs ahead of the gathers
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 enum Bar { KV_FULL = 0, KV_EMPTY = KV_FULL + MAX_STAGES,
-           RAW_FULL = KV_EMPTY + MAX_STAGES /* [NGW][NRAW] */, RAW_EMPTY = RAW_FULL + NGW * NRAW /* [NGW][NRAW] */,
-           S_FULL = RAW_EMPTY + NGW * NRAW /* [2 teams] */, S_EMPTY = S_FULL + 2, P_FULL /* [2 teams] */, PV_DONE = P_FULL + 2 /* [2 teams] */,
-           DEC = PV_DONE + 2 /* [2 teams] */, Q_FULL = DEC + 2, QT_FULL /* [2 feature halves] */, NUM_BARS = QT_FULL + 2 };
+           S_FULL = KV_EMPTY + MAX_STAGES /* [2 teams] */, S_EMPTY = S_FULL + 2 /* [2 teams] */, P_FULL = S_EMPTY + 2 /* [2 teams] */,
+           PV_DONE = P_FULL + 2 /* [2 teams] */, DEC = PV_DONE + 2 /* [2 teams] */, Q_FULL = DEC + 2, QT_FULL /* [2 feature halves] */,
+           QR_FULL = QT_FULL + 2, NUM_BARS };
 constexpr uint32_t SM_BAR = 0;
 constexpr uint32_t SM_TMEM = SM_BAR + NUM_BARS * 8;
 constexpr uint32_t SM_ABORT = SM_TMEM + 4;
 constexpr uint32_t SM_LEAVE = SM_ABORT + 4;                 // softmax warps that have left because of an abort
-constexpr uint32_t SM_MASK = 512;                           // uint8 [RING][8]: validity bits of the 8 tokens of producer warp w
+constexpr uint32_t SM_MASK = 512;                           // uint8 [RING][8]: validity bits of the block's tokens 8w .. 8w+7
 constexpr uint32_t SM_MAX = 1024;                           // float [2 teams][2 halves][64]: block maxima of a thread's 32 tokens
 constexpr uint32_t SM_MREF = SM_MAX + 1024;                 // float [2 teams][64]: reference maximum after the team's latest block
+constexpr uint32_t SM_MTRUE = SM_MREF + 512;                // float [2 teams][64]: largest logit of the team's blocks, at the end of a query
 constexpr uint32_t SM_SUM = SM_MAX + 2048;                  // float [4][64]: row sums at the end of a query
 constexpr uint32_t SM_IDX = SM_SUM + 1024;                  // int32 [NPW producer warps][RING][PROWS]
-constexpr uint32_t SM_MTRUE = SM_IDX + NPW * RING * PROWS * 4;   // float [4][64]: largest logits at the end of a query
-constexpr uint32_t SM_P = 7168;                             // two P buffers (one per team), 1024-byte aligned
+constexpr uint32_t SM_P = 6144;                             // two P buffers (one per team), 1024-byte aligned
 constexpr uint32_t SM_XCHG = SM_P + 2 * P_BYTES;            // float [2 receiving halves][64 heads][32], chunk-swizzled; also the Q tiles
-constexpr uint32_t SM_STAGE = SM_XCHG + 2 * 64 * 32 * 4;    // stages, then (decode) the raw ring
-constexpr uint32_t SM_RAW = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
-static_assert(SM_LEAVE + 4 <= SM_MASK && SM_MTRUE + 1024 <= SM_P && SM_P % 1024 == 0 && SM_STAGE % 1024 == 0 &&
-              STAGE_BYTES % 1024 == 0 && SM_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0, "shared memory map");
+constexpr uint32_t SM_QROPE = SM_XCHG + 2 * 64 * 32 * 4;    // Q's RoPE panel (A operand of the RoPE k-steps)
+constexpr uint32_t SM_STAGE = SM_QROPE + QROPE_BYTES;       // stages
+static_assert(SM_LEAVE + 4 <= SM_MASK && SM_MTRUE + 512 <= SM_SUM && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 &&
+              SM_QROPE % 1024 == 0 && SM_STAGE % 1024 == 0 && STAGE_BYTES % 1024 == 0,
+              "shared memory map");
 constexpr uint32_t SMEM_USED_PREFILL = SM_STAGE + NSTAGE_PREFILL * STAGE_BYTES;
-constexpr uint32_t SMEM_USED_DECODE = SM_RAW + NRAW * RAW_BYTES;
+constexpr uint32_t SMEM_USED_DECODE = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
 constexpr uint32_t SMEM_BYTES = (SMEM_USED_PREFILL > SMEM_USED_DECODE ? SMEM_USED_PREFILL : SMEM_USED_DECODE) + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
 
 struct Params {
-  CUtensorMap map_nope, map_rope;   // decode: byte views of the pool (256-byte NoPE box, 144-byte tail box); prefill: bf16 views of kv
-  CUtensorMap map_q, map_q_rope;   // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle) / x 32 dims
-  int q_tma;                     // the two maps above are valid; else Q is read with plain loads
+  CUtensorMap map_nope, map_rope;   // prefill: bf16 views of kv with boxes of 64 dims (128B swizzle) / 32 dims (64B swizzle)
+  CUtensorMap map_q;               // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle)
+  int q_tma;                     // the map above is valid; else Q is read with plain loads
   // decode with a second cache (extra_k_cache): its maps, geometry and index list; has_extra = 0 otherwise
-  CUtensorMap map_nope2, map_rope2;
-  int has_extra, rows_per_block2, page2, extra_topk;
+  int has_extra, page2, rows_per_block2, extra_topk;
   int64_t total_rows2;
+  const uint8_t* kv_rows2;
   const int* indices2;
   int64_t idx2_stride0, idx2_stride1;
   const int* extra_topk_length;
-  int rows_per_block;            // decode: virtual rows per cache block = block stride / 656
   int mode;                      // 0 decode, 1 prefill
   int h_q, topk;
   float scale_log2;
@@ -139,6 +136,7 @@ struct Params {
   const uint8_t* kv_rows;
   int64_t kv_stride_block;
   int page, layout;
+  int rows_per_block;            // decode: rows of the 656-byte-pitch view per cache block = block stride / 656
   int64_t total_rows;
   const SchedRecord* sched;
   const int* num_splits;
@@ -267,7 +265,6 @@ __device__ __forceinline__ uint4 lds_16(uint32_t a) {
   return v;
 }
 __device__ __forceinline__ uint32_t stage_addr(const Ctx& c, int s) { return c.base + SM_STAGE + (uint32_t)s * STAGE_BYTES; }
-__device__ __forceinline__ uint32_t raw_addr(const Ctx& c, int s) { return c.base + SM_RAW + (uint32_t)s * RAW_BYTES; }
 template <class P>
 __device__ __forceinline__ int num_stages(const P& p) { return p.mode == 0 ? NSTAGE_DECODE : NSTAGE_PREFILL; }
 
@@ -287,12 +284,7 @@ struct BlockCursor {
 // ---- TMA gathers ---------------------------------------------------------------------------------------
 // Four rows of a 2-D tensor map into four consecutive rows of shared memory (destination 128-byte aligned);
 // rows outside the tensor are zero-filled.  `col` times the element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int col, int4 rows, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::1 [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(dst), "l"(map), "r"(col), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w), "r"(bar) : "memory");
-}
-// The same gather with the completion signalled on a barrier given by a shared::cluster address, which may
+// The completion is signalled on a barrier given by a shared::cluster address, which may
 // belong to the other CTA of the pair (cta_group::2); the destination is this CTA's own shared memory.
 __device__ __forceinline__ void tma_gather4_pair(uint32_t dst, const CUtensorMap* map, int col, int4 rows, uint32_t cluster_bar) {
   asm volatile(
@@ -338,13 +330,6 @@ __device__ __forceinline__ void dequant_chunk_f16(const uint4& raw, uint32_t sca
   }
   out_lo = make_uint4(o[0], o[1], o[2], o[3]);
   out_hi = make_uint4(o[4], o[5], o[6], o[7]);
-}
-
-// In-cache row index -> row of the 656-byte-pitch view used for addressing (blocks may be padded beyond page*656 bytes).
-__device__ __forceinline__ int virtual_row(int rows_per_block, int page, int id) {
-  if (rows_per_block == page) return id;
-  const int b = id / page;
-  return b * rows_per_block + (id - b * page);
 }
 
 // ---- prefill: producer warps --------------------------------------------------------------------------------
@@ -420,144 +405,185 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
   cp_async_wait<0>();
 }
 
-// ---- decode: gather warps and converter warps -----------------------------------------------------------
-// Gather warp w (of NGW) fetches rows [32w, 32w+32) of every block into the raw ring: lane = 2 * group + piece
-// issues one TMA gather of four rows (piece = this CTA's NoPE half / the 144-byte tail with scales and RoPE).  The cache indices are read
-// with plain loads one block ahead of their use.  The eight converter warps (the producer warps) dequantise
-// eight rows each from the raw ring into the stage and tell the leader CTA.
-template <class P>
-__device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank, int gw) {
-  const int lane = threadIdx.x & 31;
-  const int q = lane >> 1, kind = lane & 1;
-  const bool active = q < 8;
-  BlockCursor ld(p, rec), gat(p, rec);
-  // the four cache indices of this lane's group in the block the cursor points at (-1 beyond the item's range)
-  auto load_idx = [&](const BlockCursor& cu, int (&id)[4]) {
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int pos = cu.it.tok_lo + cu.n * T + 32 * gw + 4 * q + k;
-      id[k] = -1;
-      if (active && cu.live && pos < cu.it.tok_hi) {
-        if (pos < cu.it.main_end) {
-          if (pos < cu.it.limit) asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(id[k]) : "l"(cu.it.idx + pos));
-        } else if (pos < cu.it.limit2) {
-          asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(id[k]) : "l"(cu.it.idx2 + (pos - cu.it.main_end)));
-        }
-      }
-    }
-  };
-  int nxt[4];
-  load_idx(ld, nxt);
-  for (uint32_t g = 0; gat.live; ++g, gat.advance(p, rec)) {
-    int id[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
-    ld.advance(p, rec);
-    load_idx(ld, nxt);                                   // in flight while this block's gathers are issued
-    const int slot = g % NRAW;
-    const uint32_t use = g / NRAW;
-    bool ok = use == 0 || wait(c, RAW_EMPTY + gw * NRAW + slot, use - 1, 12);
-    if (!__all_sync(0xffffffffu, ok)) return;
-    // a block lies entirely in the main or in the extra part of the token list (the boundary is a block multiple)
-    const bool extra = gat.it.tok_lo + gat.n * T >= gat.it.main_end;
-    const int range = extra ? (int)p.total_rows2 : (int)p.total_rows;
-    uint32_t bits = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (id[k] < 0 || id[k] >= range) { id[k] = -1; continue; }
-      if (kind == 0 && active) bits |= 1u << (4 * q + k);
-      id[k] = extra ? virtual_row(p.rows_per_block2, p.page2, id[k]) : virtual_row(p.rows_per_block, p.page, id[k]);
-    }
-    bits = __reduce_or_sync(0xffffffffu, bits);
-    const uint32_t bar = bar_addr(c, RAW_FULL + gw * NRAW + slot);
-    if (lane == 0) {
-      sts_u32(c.base + SM_MASK + 8u * (g % RING) + 4u * gw, bits);
-      mbar_expect_tx(bar, RAW_TX_BYTES / NGW);
-    }
-    __syncwarp();
-    if (active) {
-      const uint32_t dst = raw_addr(c, slot);
-      const uint32_t r0 = 32u * gw + 4u * q;
-      const uint32_t d = kind == 0 ? dst + RAW_NOPE + r0 * 256u : dst + RAW_TAIL + (r0 >> 2) * TAIL_GROUP;
-      const CUtensorMap* map = extra ? (kind == 0 ? &p.map_nope2 : &p.map_rope2) : (kind == 0 ? &p.map_nope : &p.map_rope);
-      tma_gather4(d, map, kind == 0 ? 256 * (int)rank : 512, make_int4(id[0], id[1], id[2], id[3]), bar);
-    }
-  }
-}
-
+// ---- decode: converter warps ------------------------------------------------------------------------------
+// Converter warp w (of NPW) owns tokens [PROWS*w, PROWS*(w+1)) of every block, from the cache to the MMA stage:
+//   * lanes 0-7 prefetch the tokens' cache indices into the warp's ring (4-byte cp.async, IDX_LOOKAHEAD blocks ahead);
+//   * ROW_PREFETCH blocks ahead the warp asks L2 for its rows' cache lines;
+//   * one block ahead every thread loads the pieces it will dequantise straight into registers with 16-byte loads:
+//     four 16-byte chunks of this CTA's NoPE half with their scales and one chunk of this CTA's RoPE half.  An
+//     invalid slot loads nothing and holds zeros, so it contributes exact zeros even when unused rows are NaN-poisoned;
+//   * the thread dequantises its chunks and, once the stage is free, stores them as the MMA operand; the warp then
+//     tells the leader CTA.
+struct RowRegs {                 // one thread's pieces of a block
+  uint4 nope[PROWS / 2];         // chunk lane % 16 of rows 2 it + lane / 16
+  uint32_t scale[PROWS / 2];     // V32: the fp32 scale of that chunk's 128 features; MXFP8: the e8m0 byte of its 32
+  uint4 rope;                    // chunk lane % 4 of row lane / 4
+};
+constexpr int ROW_PREFETCH = 3;
 template <class P>
 __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank) {
   const int ptid = threadIdx.x - 32 * NSW, pwarp = ptid >> 5, lane = ptid & 31;
-  const int gw = pwarp / (NPW / NGW);
-  BlockCursor cur(p, rec);
-  for (uint32_t g = 0; cur.live; ++g, cur.advance(p, rec)) {
-    const int st = g % NSTAGE_DECODE, slot = g % NRAW;
-    bool ok = wait(c, RAW_FULL + gw * NRAW + slot, g / NRAW, 14);
-    if (!__all_sync(0xffffffffu, ok)) return;
-    const uint32_t use = g / NSTAGE_DECODE;
-    ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
-    if (!__all_sync(0xffffffffu, ok)) return;
-    const uint32_t raw = raw_addr(c, slot), stage = stage_addr(c, st);
+  const uint32_t ring = c.base + SM_IDX + (uint32_t)pwarp * (RING * PROWS * 4);
+  BlockCursor feed(p, rec), pre(p, rec), ldc(p, rec), cur(p, rec);
+  const int ch = lane & 15;
+
+  auto feed_block = [&](uint32_t blk) {       // cache indices of block blk -> ring slot blk % RING; one cp.async group
+    if (feed.live) {
+      if (lane < PROWS) {
+        const int pos = feed.it.tok_lo + feed.n * T + PROWS * pwarp + lane;
+        const uint32_t dst = ring + ((blk % RING) * PROWS + lane) * 4;
+        const int* src = nullptr;
+        if (pos < feed.it.tok_hi) {
+          if (pos < feed.it.main_end) { if (pos < feed.it.limit) src = feed.it.idx + pos; }
+          else if (pos < feed.it.limit2) src = feed.it.idx2 + (pos - feed.it.main_end);
+        }
+        if (src) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+        else asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0xffffffffu) : "memory");
+      }
+      feed.advance(p, rec);
+    }
+    cp_async_commit();
+  };
+  // Row lane % 8 of block blk as a row number of its pool's 656-byte-pitch view (a cache block may be padded by whole
+  // rows), -1 = invalid; `extra` tells which pool the block's rows live in (a block lies entirely in the main or in the
+  // extra part of the token list: the boundary is a block multiple).
+  auto block_row = [&](const BlockCursor& cu, uint32_t blk, bool& extra) -> int {
+    extra = p.has_extra && cu.it.tok_lo + cu.n * T >= cu.it.main_end;
+    const int64_t total = extra ? p.total_rows2 : p.total_rows;
+    const int page = extra ? p.page2 : p.page, rpb = extra ? p.rows_per_block2 : p.rows_per_block;
+    const int id = (int)lds_u32(ring + ((blk % RING) * PROWS + (lane & 7)) * 4);
+    if (id < 0 || id >= total) return -1;
+    if (rpb == page) return id;
+    const int b = id / page;
+    return b * rpb + (id - b * page);
+  };
+  auto prefetch_block = [&](uint32_t blk) {   // ask L2 for the lines of the warp's rows: lane = 4 row + piece
+    if (!pre.live) return;
+    bool extra;
+    const int vrow = __shfl_sync(0xffffffffu, block_row(pre, blk, extra), lane >> 2);
+    if (vrow >= 0) {
+      const uint8_t* row = (extra ? p.kv_rows2 : p.kv_rows) + (int64_t)vrow * ROW_BYTES;
+      const int piece = lane & 3;            // first / second / last line of the NoPE half, the tail (scales + RoPE half)
+      const uint8_t* a = piece < 3 ? row + 256 * (int)rank + (piece == 2 ? 255 : 128 * piece) : row + ROPE_OFF + 64 * (int)rank + 63;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+      if (piece == 3) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + SCALE_OFF));
+    }
+    pre.advance(p, rec);
+  };
+  auto load_block = [&](uint32_t blk, RowRegs& r) {   // this thread's pieces of block blk; validity bits -> mask ring
+    if (!ldc.live) return;
+    bool extra;
+    const int mine = block_row(ldc, blk, extra);
+    const uint8_t* pool = extra ? p.kv_rows2 : p.kv_rows;
+    const uint32_t bits = __ballot_sync(0xffffffffu, mine >= 0) & 0xffu;
+    if (lane == 0) asm volatile("st.shared.u8 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (blk % RING) + pwarp), "r"(bits) : "memory");
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
-      const int f = 32 * it + lane, r = f >> 4, ch = f & 15;
-      const uint32_t row = (uint32_t)PROWS * pwarp + r;
-      const uint32_t sc = raw + RAW_TAIL + (row >> 2) * TAIL_GROUP + (row & 3u) * TAIL_BYTES;
-      float scale;
-      if (p.layout == FMLA_LAYOUT_V32) {
-        scale = lds_f32(sc + 4u * (2u * rank + (ch >> 3)));
-      } else {
-        uint32_t byte;
-        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(byte) : "r"(sc + 8u * rank + (ch >> 1)));
-        scale = e8m0_to_float(byte);
+      const int vrow = __shfl_sync(0xffffffffu, mine, 2 * it + (lane >> 4));
+      r.nope[it] = make_uint4(0u, 0u, 0u, 0u);
+      r.scale[it] = 0u;
+      if (vrow >= 0) {
+        const uint8_t* row = pool + (int64_t)vrow * ROW_BYTES;
+        r.nope[it] = ldg_nc_16(row + 256 * (int)rank + 16 * ch);
+        if (p.layout == FMLA_LAYOUT_V32) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r.scale[it]) : "l"(row + SCALE_OFF + 4 * (2 * (int)rank + (ch >> 3))));
+        else asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(r.scale[it]) : "l"(row + SCALE_OFF + 8 * (int)rank + (ch >> 1)));
       }
-      uint4 lo, hi;
-      dequant_chunk_f16(lds_16(raw + RAW_NOPE + row * 256u + ch * 16u), scale_to_half2(scale), lo, hi);
-      const uint32_t panel = stage + (ch >> 2) * PANEL;
-      st_shared16(panel + swz(row, 2 * (ch & 3)), lo);
-      st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi);
     }
+    const int vrow = __shfl_sync(0xffffffffu, mine, lane >> 2);
+    r.rope = make_uint4(0u, 0u, 0u, 0u);
+    if (vrow >= 0) r.rope = ldg_nc_16(pool + (int64_t)vrow * ROW_BYTES + ROPE_OFF + 64 * (int)rank + 16 * (lane & 3));
+    ldc.advance(p, rec);
+  };
+
+#pragma unroll 1
+  for (int k = 0; k < IDX_LOOKAHEAD; ++k) feed_block(k);
+  cp_async_wait<0>();
+  __syncwarp();
+#pragma unroll 1
+  for (int k = 0; k < ROW_PREFETCH; ++k) prefetch_block(k);
+  RowRegs regs;
+  load_block(0, regs);
+
+  for (uint32_t g = 0; cur.live; ++g, cur.advance(p, rec)) {
+    const int st = g % NSTAGE_DECODE;
+    const uint32_t use = g / NSTAGE_DECODE;
+    const uint32_t stage = stage_addr(c, st);
+    uint4 lo[PROWS / 2], hi[PROWS / 2];
 #pragma unroll
-    for (int it = 0; it < PROWS / 8; ++it) {
-      const int f = 32 * it + lane, r = f >> 2, ch = f & 3;
-      const uint32_t row = (uint32_t)PROWS * pwarp + r;
-      st_shared16(stage + ROPE_PANEL + row * 64u + ((ch ^ ((row >> 1) & 3u)) << 4), lds_16(raw + RAW_TAIL + (row >> 2) * TAIL_GROUP + (row & 3u) * TAIL_BYTES + 16u + 64u * rank + ch * 16u));
+    for (int it = 0; it < PROWS / 2; ++it) {
+      const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(regs.scale[it]) : e8m0_to_float(regs.scale[it]);
+      dequant_chunk_f16(regs.nope[it], scale_to_half2(scale), lo[it], hi[it]);
     }
-    // the dequantised rows (generic proxy) become visible to the MMAs, and this warp's reads of the raw slot
-    // are ordered before the TMA writes of the slot's next use
+    const uint4 rope = regs.rope;
+    // The next block's pieces are requested before the stage wait, so that they travel while this block is stored; the
+    // indices they need were fed IDX_LOOKAHEAD - 1 blocks ago (at most ROW_PREFETCH feeds may still be pending).
+    static_assert(IDX_LOOKAHEAD > ROW_PREFETCH + 1, "the index ring runs ahead of the row prefetch");
+    cp_async_wait<IDX_LOOKAHEAD - 1 - ROW_PREFETCH>();
+    __syncwarp();
+    load_block(g + 1, regs);
+    // only the stores need the stage: everything above overlaps the products that still read its previous contents
+    const bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
+    if (!__all_sync(0xffffffffu, ok)) return;
+#pragma unroll
+    for (int it = 0; it < PROWS / 2; ++it) {
+      const uint32_t row = (uint32_t)PROWS * pwarp + 2 * it + (lane >> 4);
+      const uint32_t panel = stage + (ch >> 2) * PANEL;
+      st_shared16(panel + swz(row, 2 * (ch & 3)), lo[it]);
+      st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi[it]);
+    }
+    {
+      const uint32_t row = (uint32_t)PROWS * pwarp + (lane >> 2), chr = lane & 3;
+      st_shared16(stage + ROPE_PANEL + row * 64u + ((chr ^ ((row >> 1) & 3u)) << 4), rope);
+    }
+    // the dequantised rows (generic proxy) become visible to the MMAs
     fence_async_smem();
     __syncwarp();
-    if (lane == 0) {
-      mbar_arrive(bar_addr(c, RAW_EMPTY + gw * NRAW + slot));
-      arrive_leader(c, KV_FULL + st);
-    }
+    if (lane == 0) arrive_leader(c, KV_FULL + st);
+    prefetch_block(g + ROW_PREFETCH);
+    feed_block(g + IDX_LOOKAHEAD);
   }
+  cp_async_wait<0>();
 }
 
 // ---- MMA issuers (one thread each, CTA 0) ---------------------------------------------------------
+// QK^T issuer k writes S buffer k: it takes the blocks whose running number has parity k, so consecutive blocks are
+// issued by two threads and the instruction issue of one overlaps the other's; a block's 20 products still come from
+// one thread in a fixed order, which keeps the results bitwise repeatable.
 template <class P>
-__device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem) {
+__device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem, uint32_t k) {
   // decode: NoPE k-steps are fp16 x fp16 (Q converted on load, K dequantised to fp16); RoPE k-steps are bf16
   const uint32_t idesc_nope = p.mode == 0 ? idesc_16bit(128, 2 * T, 0, 0, false, false) : idesc_bf16(128, 2 * T, false, false);
   constexpr uint32_t idesc_rope = idesc_bf16(128, 2 * T, false, false);
+  // RoPE k-steps take Q from shared memory, where both lane halves of the accumulator would see the same 16 features;
+  // the products of feature half 0 therefore leave lanes 64-127 untouched and those of half 1 lanes 0-63
+  const uint32_t F = 0xffffffffu;
+  const uint32_t keep_upper[8] = {0u, 0u, F, F, 0u, 0u, F, F}, keep_lower[8] = {F, F, 0u, 0u, F, F, 0u, 0u};
   const int nst = num_stages(p);
+  const uint32_t s_tmem = tmem + TM_S + 64u * k;
+  const uint64_t qr0 = smem_desc_kmajor(c.base + SM_QROPE);
   Item it;
   uint32_t seq = 0;
   for (int i = 0; get_item(p, rec, i, it); ++i) {
     if (!wait(c, Q_FULL, i, 21)) return;
-    const int nb = num_blocks(it);
-    for (int n = 0; n < nb; ++n, ++seq) {
+    const uint32_t seq_end = seq + (uint32_t)num_blocks(it);
+    for (seq += (seq ^ k) & 1u; seq < seq_end; seq += 2) {
       const int s = seq % nst;
       if (!wait(c, KV_FULL + s, seq / nst, 22)) return;
-      if (seq > 0 && !wait(c, S_EMPTY, seq - 1, 23)) return;
+      if (seq >= 2 && !wait(c, S_EMPTY + k, (seq >> 1) - 1, 23)) return;
       tc_fence_after_sync();
       const uint64_t b0 = smem_desc_kmajor(stage_addr(c, s));
       const uint64_t r0 = smem_desc_kmajor_sw64(stage_addr(c, s) + ROPE_PANEL);
 #pragma unroll
-      for (int j = 0; j < 18; ++j) {
-        const uint64_t bd = j < 16 ? b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4) : r0 + (((j - 16) * 32) >> 4);
-        umma_ts<2>(tmem + TM_S, tmem + TM_Q + 8 * j, bd, j < 16 ? idesc_nope : idesc_rope, j > 0);
+      for (int j = 0; j < 16; ++j)
+        umma_ts<2>(s_tmem, tmem + TM_Q + 8 * j, b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4), idesc_nope, j > 0);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        umma_ss_pair_masked(s_tmem, qr0 + ((j * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_upper);
+        umma_ss_pair_masked(s_tmem, qr0 + (((2 + j) * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_lower);
       }
-      umma_commit<2>(bar_addr(c, S_FULL + (seq & 1)), 0x3);
+      umma_commit<2>(bar_addr(c, S_FULL + k), 0x3);
     }
+    seq = seq_end;
   }
 }
 
@@ -630,11 +656,12 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Q of one query -> tensor memory.  Lanes 0-63 take Q[head, NoPE 0:256 | RoPE 0:32], lanes 64-127 take
-// Q[head, NoPE 256:512 | RoPE 32:64]; column c of the Q region holds elements (2c, 2c+1) of the lane's 288.
-// Column group g of a lane loads NoPE columns 64g .. 64g+63 and RoPE columns 128+8g .. 128+8g+7.
+// Q of one query -> tensor memory (NoPE) and shared memory (RoPE) with plain loads.  Lanes 0-63 take Q[head, NoPE 0:256],
+// lanes 64-127 take Q[head, NoPE 256:512]; column c of the Q region holds elements (2c, 2c+1) of the lane's 256.
+// Column group g of a lane loads NoPE columns 64g .. 64g+63; the thread also writes RoPE dims 32 half + 16 g .. + 15
+// of its head into the 128B-swizzled RoPE panel.
 template <class P>
-__device__ __forceinline__ void load_q_to_tmem(const P& p, const Item& it, uint32_t tmem_lane, int head, int half, int g) {
+__device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head, int h, int half, int g) {
   const __nv_bfloat16* row = it.q + (int64_t)head * p.q_stride_h;
   const __nv_bfloat16* nope = row + 256 * half + 128 * g;
   const __nv_bfloat16* rope = row + 512 + 32 * half + 16 * g;
@@ -666,8 +693,9 @@ __device__ __forceinline__ void load_q_to_tmem(const P& p, const Item& it, uint3
     for (int k = 0; k < 32; ++k) r[k] = bf16x2_to_f16x2(r[k]);
   }
   tmem_st32(tmem_lane + TM_Q + 64 * g + 32, r);
-  const uint32_t r8[8] = {e[0].x, e[0].y, e[0].z, e[0].w, e[1].x, e[1].y, e[1].z, e[1].w};
-  tmem_st8(tmem_lane + TM_Q + 128 + 8 * g, r8);
+  st_shared16(c.base + SM_QROPE + swz(h, 4 * half + 2 * g), e[0]);
+  st_shared16(c.base + SM_QROPE + swz(h, 4 * half + 2 * g + 1), e[1]);
+  fence_async_smem();      // the panel is read by the MMAs (async proxy)
   tmem_st_wait();
 }
 // 4-D tile load into this CTA's shared memory, completion on a local mbarrier.
@@ -679,33 +707,35 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map
 // The 128 softmax threads of one feature half (four warps) meet here while they load Q.
 __device__ __forceinline__ void half_sync(int half) { asm volatile("bar.sync %0, 128;" ::"r"(7 + half) : "memory"); }
 
-// Q of one query -> tensor memory through shared memory: the 64 heads x 288 dims of a feature half arrive as
-// five TMA tiles (four of 64 NoPE dims, one of 32 RoPE dims) in that half's 8 KB of the exchange buffer, which is
-// idle between two work items; each thread copies its 32 (16) dims of the tile to its tensor-memory lane.  The
-// next tile is requested as soon as all 128 threads of the half have read the current one.
-// `uses` counts the tiles this thread has waited for (barrier parity).  Returns false when aborting.
-// `pre()` runs while the first tile is in flight (false = aborting) and `post(r)` after NoPE tile r has been copied:
-// the caller uses them to run the previous item's epilogue in the shadow of the tiles' latency.
+// Q of one query through TMA.  RoPE: the 64 heads x 64 dims go straight into the RoPE panel, where the MMAs read them.
+// NoPE: the 64 heads x 256 dims of a feature half arrive as four tiles of 64 dims in that half's 8 KB of the exchange
+// buffer, which is idle between two work items; each thread copies its 32 dims of the tile to its tensor-memory lane,
+// and the next tile is requested as soon as all 128 threads of the half have read the current one.
+// `uses` counts the NoPE tiles this thread has waited for and `items` the RoPE tiles (barrier parities).  Returns false
+// when aborting.  `pre()` runs while the first tiles are in flight (false = aborting) and `post(r)` after NoPE tile r
+// has been copied: the caller uses them to run the previous item's epilogue in the shadow of the tiles' latency.
 template <class P, class Pre, class Post>
 __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head0, int h, int half,
-                                           int g, bool issuer, uint32_t& uses, Pre pre, Post post) {
+                                           int g, bool issuer, uint32_t& uses, uint32_t& items, Pre pre, Post post) {
   const uint32_t buf = c.base + SM_XCHG + 8192u * half;
-  const uint32_t bar = bar_addr(c, QT_FULL + half);
+  const uint32_t bar = bar_addr(c, QT_FULL + half), bar_rope = bar_addr(c, QR_FULL);
   const int c2 = p.mode == 0 ? it.sq : it.req, c3 = p.mode == 0 ? it.req : 0;
   auto request = [&](int r) {
-    if (r < 4) {
-      mbar_expect_tx(bar, 64 * 128);
-      tma_tile_4d(buf, &p.map_q, 256 * half + 64 * r, head0, c2, c3, bar);
-    } else {
-      mbar_expect_tx(bar, 64 * 64);
-      tma_tile_4d(buf, &p.map_q_rope, 512 + 32 * half, head0, c2, c3, bar);
-    }
+    mbar_expect_tx(bar, 64 * 128);
+    tma_tile_4d(buf, &p.map_q, 256 * half + 64 * r, head0, c2, c3, bar);
   };
-  // every softmax warp has finished with the exchange buffer (last block's partial sums) before a tile overwrites
-  // it; each thread orders its own generic-proxy accesses to the buffer before the TMA writes that follow the barrier
+  // Every softmax warp has consumed the query's last S, so its QK^T products are complete and Q may be replaced; and
+  // every warp has finished with the exchange buffer (last block's partial sums) before a tile overwrites it: each
+  // thread orders its own generic-proxy accesses to the buffer before the TMA writes that follow the barrier.
   fence_async_smem();
   asm volatile("bar.sync 9, 256;" ::: "memory");
-  if (issuer) request(0);
+  if (issuer) {
+    if (half == 0) {
+      mbar_expect_tx(bar_rope, QROPE_BYTES);
+      tma_tile_4d(c.base + SM_QROPE, &p.map_q, 512, head0, c2, c3, bar_rope);
+    }
+    request(0);
+  }
   if (!pre()) return false;
 #pragma unroll 1
   for (int r = 0; r < 4; ++r) {
@@ -717,9 +747,9 @@ __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item&
       const uint4 t = lds_16(buf + swz(h, 4 * g + k));
       v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
     }
-    fence_async_smem();      // my reads of this tile before the next tile's TMA writes
+    fence_async_smem();      // my reads of this tile before the next tile's TMA writes (or the block loop's stores)
     half_sync(half);
-    if (issuer) request(r + 1);
+    if (issuer && r < 3) request(r + 1);
     if (p.mode == 0) {   // decode multiplies the NoPE part in fp16
 #pragma unroll
       for (int k = 0; k < 16; ++k) v[k] = bf16x2_to_f16x2(v[k]);
@@ -727,14 +757,8 @@ __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item&
     tmem_st16(tmem_lane + TM_Q + 32 * r + 16 * g, v);
     post(r);
   }
-  if (!mbar_wait_abortable(bar, uses & 1u, c.abort_flag)) { if (*c.abort_flag == 0) raise_abort(c, 48); return false; }
-  ++uses;
-  {
-    const uint4 t0 = lds_16(buf + h * 64u + 32u * g), t1 = lds_16(buf + h * 64u + 32u * g + 16u);
-    const uint32_t v8[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-    tmem_st8(tmem_lane + TM_Q + 128 + 8 * g, v8);
-  }
-  half_sync(half);      // the exchange buffer is free again for the block loop
+  if (!mbar_wait_abortable(bar_rope, items & 1u, c.abort_flag)) { if (*c.abort_flag == 0) raise_abort(c, 49); return false; }
+  ++items;
   tmem_st_wait();
   return true;
 }
@@ -776,12 +800,12 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   bool have = get_item(p, rec, 0, it);
   const int head0 = blockIdx.z * 128 + (int)rank * 64;
   const bool q_issuer = h == 0 && g == 0;
-  uint32_t qt_uses = 0;
+  uint32_t qt_uses = 0, qr_items = 0;
   if (have) {
     if (p.q_tma) {
-      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
+      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
     } else {
-      load_q_to_tmem(p, it, tmem_lane, head, half, g);
+      load_q_to_tmem(p, c, it, tmem_lane, head, h, half, g);
     }
     tc_fence_before_sync();
     __syncwarp();
@@ -805,17 +829,17 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       uint32_t keep[32];
       {
         uint32_t send[32];
-        tmem_ld32(tmem_lane + TM_S + 32 * (1 - half), send);
+        tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * (1 - half), send);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           st_shared16(xchg_put + (((uint32_t)k ^ xsw) << 4), make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
       }
-      tmem_ld32(tmem_lane + TM_S + 32 * half, keep);
+      tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * half, keep);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) arrive_leader(c, S_EMPTY);
+      if (lane == 0) arrive_leader(c, S_EMPTY + team);
       pair_sync(warp);
       float x[32];
 #pragma unroll
@@ -908,13 +932,13 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     auto epi_begin = [&]() -> bool {            // row sums and maxima of the quad, output scale, destination
       m_fin = lds_f32(c.base + SM_MREF + 4u * (64 * (last & 1u) + h));
       sts_f32(sum_base + 256u * slot, m_mine == m_fin ? l_sum : l_sum * exp2f(m_mine - m_fin));
-      sts_f32(mtrue_base + 256u * slot, m_true);
+      if (half == 0) sts_f32(mtrue_base + 256u * team, m_true);   // the two halves of a team hold the same value
       bool ok = wait(c, PV_DONE + (last & 1), last >> 1, 47);
       if (!__all_sync(0xffffffffu, ok)) return false;
       tc_fence_after_sync();
       quad_sync(warp);
       const float l_tot = (lds_f32(sum_base) + lds_f32(sum_base + 256u)) + (lds_f32(sum_base + 512u) + lds_f32(sum_base + 768u));
-      m_true = fmaxf(fmaxf(lds_f32(mtrue_base), lds_f32(mtrue_base + 256u)), fmaxf(lds_f32(mtrue_base + 512u), lds_f32(mtrue_base + 768u)));
+      m_true = fmaxf(lds_f32(mtrue_base), lds_f32(mtrue_base + 256u));
       empty = l_tot == 0.f;
       lse2 = empty ? -CUDART_INF_F : m_fin + log2f(l_tot);
       if (it.split) mul = empty ? 0.f : 1.f / l_tot;
@@ -961,14 +985,14 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     // With the TMA path the epilogue's four chunks run between the Q tiles, in the shadow of their latency;
     // either way the next item's first QK^T overlaps the rest of the epilogue.
     if (have_next && p.q_tma) {
-      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
+      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(c, Q_FULL);
     } else {
       asm volatile("bar.sync 9, 256;" ::: "memory");
       if (have_next) {
-        load_q_to_tmem(p, it_next, tmem_lane, head, half, g);
+        load_q_to_tmem(p, c, it_next, tmem_lane, head, h, half, g);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) arrive_leader(c, Q_FULL);
@@ -1012,17 +1036,14 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
       mbar_init(bar_addr(c, KV_FULL + s), 2 * NPW);    // the producer warps of both CTAs
       mbar_init(bar_addr(c, KV_EMPTY + s), 1);
     }
-    for (int s = 0; s < NGW * NRAW; ++s) {
-      mbar_init(bar_addr(c, RAW_FULL + s), 1);               // the gather warp's expect_tx arrival + the bytes
-      mbar_init(bar_addr(c, RAW_EMPTY + s), NPW / NGW);      // the converter warps that read this half of the slot
-    }
-    mbar_init(bar_addr(c, S_EMPTY), NSW);                // the warps of one softmax team in both CTAs
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_addr(c, S_FULL + b), 1);
+      mbar_init(bar_addr(c, S_EMPTY + b), NSW);              // the warps of one softmax team in both CTAs
       mbar_init(bar_addr(c, P_FULL + b), NSW);
       mbar_init(bar_addr(c, PV_DONE + b), 1);
-      mbar_init(bar_addr(c, DEC + b), NSW / 2);          // the warps of one team of this CTA
+      mbar_init(bar_addr(c, DEC + b), NSW / 2);              // the warps of one team of this CTA
     }
+    mbar_init(bar_addr(c, QR_FULL), 1);
     mbar_init(bar_addr(c, Q_FULL), 2 * NSW);
     for (int hf = 0; hf < 2; ++hf) mbar_init(bar_addr(c, QT_FULL + hf), 1);
     mbar_init_fence();
@@ -1048,11 +1069,9 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
     reg_dec<REGS_ISSUER>();
     if (warp < GATHER_WARP) {
       if (rank == 0 && (threadIdx.x & 31) == 0) {
-        if (warp == QK_WARP) issue_qk(p, rec, c, tmem);
+        if (warp < PV_WARP) issue_qk(p, rec, c, tmem, (uint32_t)(warp - QK_WARP));
         else issue_pv(p, rec, c, tmem);
       }
-    } else if (p.mode == 0) {
-      gather_role(p, rec, c, rank, warp - GATHER_WARP);
     }
   }
 
@@ -1149,6 +1168,15 @@ int tc_decode_plan(int num_sms, int h_q, int s_q, int* num_sm_parts, int* fixed_
   return FMLA_OK;
 }
 
+// Preconditions of the tensor-core decode kernel beyond the head count.
+bool tc_decode_supported(const FmlaDecodeArgs& a) {
+  auto pool_ok = [](int64_t stride, int64_t blocks, int64_t page) {
+    return stride % ROW_BYTES == 0 && (uint64_t)(blocks - 1) * (uint64_t)(stride / ROW_BYTES) + (uint64_t)page <= 0x7fffffffull;
+  };
+  if (!(a.sm_scale > 0.f) || !pool_ok(a.kv_stride_block, a.num_blocks, a.page_block_size)) return false;
+  return a.extra_kv == nullptr || pool_ok(a.extra_kv_stride_block, a.extra_num_blocks, a.extra_page_block_size);
+}
+
 int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   tc::Params p = {};
   p.mode = 0;
@@ -1157,8 +1185,7 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.sm_scale * LOG2E;
   p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
   p.q_stride0 = a.q_stride_b; p.q_stride1 = a.q_stride_s; p.q_stride_h = a.q_stride_h;
-  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B) &&
-            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   p.indices = a.indices; p.idx_stride0 = a.idx_stride_b; p.idx_stride1 = a.idx_stride_s;
   p.topk_length = a.topk_length; p.attn_sink = a.attn_sink;
   p.kv_rows = reinterpret_cast<const uint8_t*>(a.kv);
@@ -1171,33 +1198,22 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   p.lse = a.lse; p.lse_stride0 = a.lse_stride_b; p.lse_stride1 = a.lse_stride_s;
   p.o_accum = a.o_accum; p.lse_accum = a.lse_accum;
   p.status = a.status;
-  // The gather addresses rows as base + row * 656, so a block stride must be a whole number of rows
-  // (the reference has the same requirement, csrc/sm100/decode/head64/kernel.cuh:911-912).
-  FMLA_REQUIRE(a.kv_stride_block % ROW_BYTES == 0, FMLA_ERR_UNSUPPORTED,
-               "sparse_decode: the tensor-core kernel needs the KV block stride (%lld bytes) to be a multiple of 656",
-               (long long)a.kv_stride_block);
+  // Rows are addressed as base + row * 656 with a 32-bit row number, so a block stride must be a whole number of rows
+  // (the reference has the same requirement, csrc/sm100/decode/head64/kernel.cuh:911-912); tc_decode_supported() tells
+  // the caller, which then takes the CUDA-core kernel.
+  FMLA_REQUIRE(tc_decode_supported(a), FMLA_ERR_UNSUPPORTED,
+               "sparse_decode: the tensor-core kernel needs KV block strides that are multiples of 656 bytes and at most 2^31 rows "
+               "per cache (got strides %lld / %lld)", (long long)a.kv_stride_block, (long long)a.extra_kv_stride_block);
   p.rows_per_block = (int)(a.kv_stride_block / ROW_BYTES);
-  const uint64_t vrows = (uint64_t)(a.num_blocks - 1) * p.rows_per_block + a.page_block_size;
-  FMLA_REQUIRE(vrows <= 0x7fffffffull, FMLA_ERR_UNSUPPORTED, "sparse_decode: the cache spans more rows than an int32 coordinate");
-  if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows, ROW_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
-  if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows, ROW_BYTES, tc::TAIL_BYTES, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
   if (a.extra_kv != nullptr) {
-    FMLA_REQUIRE(a.extra_kv_stride_block % ROW_BYTES == 0, FMLA_ERR_UNSUPPORTED,
-                 "sparse_decode: the tensor-core kernel needs the extra KV block stride (%lld bytes) to be a multiple of 656",
-                 (long long)a.extra_kv_stride_block);
     p.has_extra = 1;
+    p.kv_rows2 = reinterpret_cast<const uint8_t*>(a.extra_kv);
     p.rows_per_block2 = (int)(a.extra_kv_stride_block / ROW_BYTES);
     p.page2 = (int)a.extra_page_block_size;
     p.total_rows2 = a.extra_num_blocks * a.extra_page_block_size;
     p.extra_topk = a.extra_topk;
     p.extra_topk_length = a.extra_topk_length;
     p.indices2 = a.extra_indices; p.idx2_stride0 = a.extra_idx_stride_b; p.idx2_stride1 = a.extra_idx_stride_s;
-    const uint64_t vrows2 = (uint64_t)(a.extra_num_blocks - 1) * p.rows_per_block2 + a.extra_page_block_size;
-    FMLA_REQUIRE(vrows2 <= 0x7fffffffull, FMLA_ERR_UNSUPPORTED, "sparse_decode: the extra cache spans more rows than an int32 coordinate");
-    if (int rc = tc::make_row_map(&p.map_nope2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows2, ROW_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
-    if (int rc = tc::make_row_map(&p.map_rope2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows2, ROW_BYTES, tc::TAIL_BYTES, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
-  } else {
-    p.map_nope2 = p.map_nope; p.map_rope2 = p.map_rope;      // never used; kept valid
   }
   return tc::launch(p, dim3(2 * a.num_sm_parts, a.s_q, (a.h_q + 127) / 128), stream);
 }
@@ -1210,8 +1226,7 @@ int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.sm_scale * LOG2E;
   p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
   p.q_stride0 = a.q_stride_s; p.q_stride1 = 0; p.q_stride_h = a.q_stride_h;
-  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 64, CU_TENSOR_MAP_SWIZZLE_128B) &&
-            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   p.indices = a.indices; p.idx_stride0 = a.idx_stride_s; p.idx_stride1 = 0;
   p.topk_length = a.topk_length; p.attn_sink = a.attn_sink;
   p.kv_bf16 = reinterpret_cast<const __nv_bfloat16*>(a.kv);
