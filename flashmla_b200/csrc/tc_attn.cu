@@ -64,30 +64,45 @@ constexpr int T = 64;                 // index slots per block
 constexpr int NPW = 8;                // producer warps per CTA
 constexpr int PROWS = 64 / NPW;       // tokens of a block owned by one producer warp
 constexpr int NSW = 8;                // softmax warps per CTA: two teams of four (one warp per quarter of the tensor-memory lanes)
-// warps: NSW softmax, NPW producers / converters, two QK^T issuers (one per S buffer), the PV issuer, one idle warp
-constexpr int QK_WARP = NSW + NPW, PV_WARP = QK_WARP + 2, GATHER_WARP = PV_WARP + 1;
-constexpr int THREADS = 32 * (GATHER_WARP + 1);   // the last warp only fills the issuers' warpgroup
-constexpr int NSTAGE_DECODE = 5, NSTAGE_PREFILL = 5, MAX_STAGES = 5;
+constexpr int NGW = 4;                // decode: gather warps, each fetching 16 of a block's 64 rows
+constexpr int GROWS = 64 / NGW;       // rows of a block fetched by one gather warp
+// warps: NSW softmax, NPW producers / converters, two QK^T issuers (one per S buffer), the PV issuer and an idle warp,
+// NGW gather warps (decode only)
+constexpr int QK_WARP = NSW + NPW, PV_WARP = QK_WARP + 2, GATHER_WARP = QK_WARP + 4;
+// decode runs all warps; prefill has no gather warps (24 / 20 warps)
+constexpr int threads_of(int mode) { return 32 * (GATHER_WARP + (mode == 0 ? NGW : 0)); }
+constexpr int NSTAGE_DECODE = 3, NSTAGE_PREFILL = 5, NRAW = 3, MAX_STAGES = 5;
 constexpr uint32_t PANEL = T * 128;                 // one 128B-swizzled [64 tokens x 64 dims] panel
 constexpr uint32_t ROPE_PANEL = 4 * PANEL;          // offset of the 64B-swizzled [64 x 32] RoPE panel in a stage
 constexpr uint32_t STAGE_BYTES = 4 * PANEL + T * 64;
 constexpr uint32_t STAGE_TX_BYTES = T * (512 + 64);
+// raw slot (decode): 64 rows x 256 NoPE bytes of this CTA's feature half; then per group of four rows the rows' 16-byte
+// scale fields (bytes 512..527) and this CTA's 64-byte RoPE halves; groups are spaced so that every gather destination
+// is 128-byte aligned
+constexpr uint32_t RAW_NOPE = 0, RAW_SCALE = T * 256, SCALE_GROUP = 128, RAW_ROPE = RAW_SCALE + (T / 4) * SCALE_GROUP, ROPE_GROUP = 256;
+constexpr uint32_t RAW_BYTES = (RAW_ROPE + (T / 4) * ROPE_GROUP + 1023) / 1024 * 1024;
+constexpr uint32_t RAW_TX_BYTES = GROWS * (256 + 16 + 64);      // bytes one gather warp brings per block
 constexpr uint32_t P_BYTES = 64 * 128;
 constexpr uint32_t QROPE_BYTES = 64 * 128;          // Q's RoPE part of this CTA's 64 heads: one 128B-swizzled [64 x 64] panel
 // tensor memory: O | Q (NoPE half of the lane: 256 dims, two per column) | two S buffers
 constexpr uint32_t TM_O = 0, TM_Q = 256, TM_S = 384, TM_COLS = 512;
 // Registers per thread after the warpgroups have re-divided the register file.  The pool is what the launch gave the
-// CTA (96 per thread, the most that 640 threads can have), not the SM's whole file: an increase beyond it never returns.
-constexpr int REGS_LAUNCH = 96, REGS_SOFTMAX = 128, REGS_PRODUCER = 80, REGS_ISSUER = 64;
-static_assert(NSW * REGS_SOFTMAX + NPW * REGS_PRODUCER + 4 * REGS_ISSUER <= (NSW + NPW + 4) * REGS_LAUNCH, "register pool");
-static_assert(NSW % 4 == 0 && NPW % 4 == 0 && THREADS == 32 * (NSW + NPW + 4), "roles fill whole warpgroups");
+// CTA (80 per thread with 768 threads, 96 with 640: the most they can have), not the SM's whole file: an increase
+// beyond it never returns.
+constexpr int REGS_SOFTMAX = 128, REGS_GATHER = 40;
+constexpr int regs_launch(int mode) { return mode == 0 ? 80 : 96; }
+constexpr int regs_producer(int mode) { return mode == 0 ? 64 : 80; }
+constexpr int regs_issuer(int mode) { return mode == 0 ? 56 : 64; }
+static_assert(NSW * REGS_SOFTMAX + NPW * regs_producer(0) + 4 * regs_issuer(0) + NGW * REGS_GATHER <= (NSW + NPW + 4 + NGW) * regs_launch(0) &&
+              NSW * REGS_SOFTMAX + NPW * regs_producer(1) + 4 * regs_issuer(1) <= (NSW + NPW + 4) * regs_launch(1), "register pool");
+static_assert(NSW % 4 == 0 && NPW % 4 == 0 && NGW % 4 == 0, "roles fill whole warpgroups");
 constexpr float RESCALE_THRESHOLD = 6.f;   // log2 units the block maximum may exceed the reference maximum
 constexpr int RING = 8;                    // slots of the index and validity-mask rings
 constexpr int IDX_LOOKAHEAD = 6;           // prefill: blocks the index prefetch runs ahead of the gathers
 
 // shared-memory map (offsets from a 1024-byte aligned base)
-enum Bar { KV_FULL = 0, KV_EMPTY = KV_FULL + MAX_STAGES,
-           S_FULL = KV_EMPTY + MAX_STAGES /* [2 teams] */, S_EMPTY = S_FULL + 2 /* [2 teams] */, P_FULL = S_EMPTY + 2 /* [2 teams] */,
+enum Bar { KV_FULL = 0, KV_EMPTY = KV_FULL + MAX_STAGES, RAW_FULL = KV_EMPTY + MAX_STAGES /* [NGW][NRAW] */, RAW_EMPTY = RAW_FULL + NGW * NRAW /* [NGW][NRAW] */,
+           S_FULL = RAW_EMPTY + NGW * NRAW /* [2 teams] */, S_EMPTY = S_FULL + 2 /* [2 teams] */, P_FULL = S_EMPTY + 2 /* [2 teams] */,
            PV_DONE = P_FULL + 2 /* [2 teams] */, DEC = PV_DONE + 2 /* [2 teams] */, Q_FULL = DEC + 2, QT_FULL /* [2 feature halves] */,
            QR_FULL = QT_FULL + 2, NUM_BARS };
 constexpr uint32_t SM_BAR = 0;
@@ -95,25 +110,29 @@ constexpr uint32_t SM_TMEM = SM_BAR + NUM_BARS * 8;
 constexpr uint32_t SM_ABORT = SM_TMEM + 4;
 constexpr uint32_t SM_LEAVE = SM_ABORT + 4;                 // softmax warps that have left because of an abort
 constexpr uint32_t SM_MASK = 512;                           // uint8 [RING][8]: validity bits of the block's tokens 8w .. 8w+7
+constexpr uint32_t SM_XFLAG = SM_MASK + RING * 8;           // uint8 [NGW][RING] (decode over two caches): the block's rows live in the extra cache
 constexpr uint32_t SM_MAX = 1024;                           // float [2 teams][2 halves][64]: block maxima of a thread's 32 tokens
 constexpr uint32_t SM_MREF = SM_MAX + 1024;                 // float [2 teams][64]: reference maximum after the team's latest block
 constexpr uint32_t SM_MTRUE = SM_MREF + 512;                // float [2 teams][64]: largest logit of the team's blocks, at the end of a query
 constexpr uint32_t SM_SUM = SM_MAX + 2048;                  // float [4][64]: row sums at the end of a query
-constexpr uint32_t SM_IDX = SM_SUM + 1024;                  // int32 [NPW producer warps][RING][PROWS]
+constexpr uint32_t SM_IDX = SM_SUM + 1024;                  // int32 [NPW producer warps][RING][PROWS] / [NGW gather warps][RING][GROWS]
 constexpr uint32_t SM_P = 6144;                             // two P buffers (one per team), 1024-byte aligned
 constexpr uint32_t SM_XCHG = SM_P + 2 * P_BYTES;            // float [2 receiving halves][64 heads][32], chunk-swizzled; also the Q tiles
 constexpr uint32_t SM_QROPE = SM_XCHG + 2 * 64 * 32 * 4;    // Q's RoPE panel (A operand of the RoPE k-steps)
-constexpr uint32_t SM_STAGE = SM_QROPE + QROPE_BYTES;       // stages
-static_assert(SM_LEAVE + 4 <= SM_MASK && SM_MTRUE + 512 <= SM_SUM && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 &&
-              SM_QROPE % 1024 == 0 && SM_STAGE % 1024 == 0 && STAGE_BYTES % 1024 == 0,
+constexpr uint32_t SM_STAGE = SM_QROPE + QROPE_BYTES;       // stages, then (decode) the raw ring
+constexpr uint32_t SM_RAW = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
+static_assert(SM_LEAVE + 4 <= SM_MASK && SM_XFLAG + NPW * RING <= SM_MAX && SM_MTRUE + 512 <= SM_SUM && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 &&
+              SM_QROPE % 1024 == 0 && SM_STAGE % 1024 == 0 && STAGE_BYTES % 1024 == 0 && SM_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0 && SM_BAR + 8 * NUM_BARS + 12 <= SM_MASK,
               "shared memory map");
 constexpr uint32_t SMEM_USED_PREFILL = SM_STAGE + NSTAGE_PREFILL * STAGE_BYTES;
-constexpr uint32_t SMEM_USED_DECODE = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
+constexpr uint32_t SMEM_USED_DECODE = SM_RAW + NRAW * RAW_BYTES;
 constexpr uint32_t SMEM_BYTES = (SMEM_USED_PREFILL > SMEM_USED_DECODE ? SMEM_USED_PREFILL : SMEM_USED_DECODE) + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
 
 struct Params {
-  CUtensorMap map_nope, map_rope;   // prefill: bf16 views of kv with boxes of 64 dims (128B swizzle) / 32 dims (64B swizzle)
+  CUtensorMap map_nope, map_rope;   // decode: byte views of the pool (256-byte NoPE box, 64-byte RoPE box); prefill: bf16 views of kv (64 / 32 dims)
+  CUtensorMap map_scale;            // decode: byte view of the pool with a 16-byte box (the scale field of a row)
+  CUtensorMap map_nope2, map_rope2, map_scale2;   // the same for the extra cache
   CUtensorMap map_q;               // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle)
   int q_tma;                     // the map above is valid; else Q is read with plain loads
   // decode with a second cache (extra_k_cache): its maps, geometry and index list; has_extra = 0 otherwise
@@ -282,6 +301,13 @@ struct BlockCursor {
 };
 
 // ---- TMA gathers ---------------------------------------------------------------------------------------
+// Four rows of a 2-D tensor map into four consecutive rows of this CTA's shared memory (destination 128-byte aligned),
+// completion on a local mbarrier; rows outside the tensor are zero-filled.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int col, int4 rows, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::1 [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(dst), "l"(map), "r"(col), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w), "r"(bar) : "memory");
+}
 // Four rows of a 2-D tensor map into four consecutive rows of shared memory (destination 128-byte aligned);
 // rows outside the tensor are zero-filled.  `col` times the element size must be a multiple of 16 bytes.
 // The completion is signalled on a barrier given by a shared::cluster address, which may
@@ -405,33 +431,34 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
   cp_async_wait<0>();
 }
 
-// ---- decode: converter warps ------------------------------------------------------------------------------
-// Converter warp w (of NPW) owns tokens [PROWS*w, PROWS*(w+1)) of every block, from the cache to the MMA stage:
-//   * lanes 0-7 prefetch the tokens' cache indices into the warp's ring (4-byte cp.async, IDX_LOOKAHEAD blocks ahead);
-//   * ROW_PREFETCH blocks ahead the warp asks L2 for its rows' cache lines;
-//   * one block ahead every thread loads the pieces it will dequantise straight into registers with 16-byte loads:
-//     four 16-byte chunks of this CTA's NoPE half with their scales and one chunk of this CTA's RoPE half.  An
-//     invalid slot loads nothing and holds zeros, so it contributes exact zeros even when unused rows are NaN-poisoned;
-//   * the thread dequantises its chunks and, once the stage is free, stores them as the MMA operand; the warp then
-//     tells the leader CTA.
-struct RowRegs {                 // one thread's pieces of a block
-  uint4 nope[PROWS / 2];         // chunk lane % 16 of rows 2 it + lane / 16
-  uint32_t scale[PROWS / 2];     // V32: the fp32 scale of that chunk's 128 features; MXFP8: the e8m0 byte of its 32
-  uint4 rope;                    // chunk lane % 4 of row lane / 4
-};
-constexpr int ROW_PREFETCH = 3;
+// ---- decode: gather warps and converter warps ---------------------------------------------------------
+// Gather warp w (of NGW) brings rows [GROWS*w, GROWS*(w+1)) of every block into the raw ring:
+//   * lanes 0-15 prefetch the rows' cache indices into the warp's ring (4-byte cp.async, IDX_LOOKAHEAD blocks ahead);
+//   * once the raw slot is free, lane = 4 piece + group (12 lanes) issues one TMA gather of four rows: piece 0 = this
+//     CTA's NoPE half (256 bytes per row), 1 = this CTA's RoPE half (64 bytes), 2 = the scale field (16 bytes).  An
+//     invalid slot gets row -1, which the TMA unit zero-fills, so it contributes exact zeros even when unused rows are
+//     NaN-poisoned.
+// A gather costs its issuing warp some 70 cycles whatever the lane, and warps issue in parallel: hence four warps.
+// The eight converter warps dequantise eight rows each from the raw ring into the stage and tell the leader CTA.
 template <class P>
-__device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank) {
-  const int ptid = threadIdx.x - 32 * NSW, pwarp = ptid >> 5, lane = ptid & 31;
-  const uint32_t ring = c.base + SM_IDX + (uint32_t)pwarp * (RING * PROWS * 4);
-  BlockCursor feed(p, rec), pre(p, rec), ldc(p, rec), cur(p, rec);
-  const int ch = lane & 15;
-
+__device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank, int gw) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t ring = c.base + SM_IDX + (uint32_t)gw * (RING * GROWS * 4);
+  const uint32_t flags = c.base + SM_XFLAG + (uint32_t)gw * RING;     // per block: its rows live in the extra cache
+  BlockCursor feed(p, rec);
+  uint32_t total_blocks = 0;
+  {
+    Item it;
+    for (int i = 0; get_item(p, rec, i, it); ++i) total_blocks += (uint32_t)num_blocks(it);
+  }
   auto feed_block = [&](uint32_t blk) {       // cache indices of block blk -> ring slot blk % RING; one cp.async group
     if (feed.live) {
-      if (lane < PROWS) {
-        const int pos = feed.it.tok_lo + feed.n * T + PROWS * pwarp + lane;
-        const uint32_t dst = ring + ((blk % RING) * PROWS + lane) * 4;
+      // a block lies entirely in the main or in the extra part of the token list (the boundary is a block multiple)
+      if (p.has_extra && lane == 0)
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(flags + blk % RING), "r"(feed.it.tok_lo + feed.n * T >= feed.it.main_end ? 1u : 0u) : "memory");
+      if (lane < GROWS) {
+        const int pos = feed.it.tok_lo + feed.n * T + GROWS * gw + lane;
+        const uint32_t dst = ring + ((blk % RING) * GROWS + lane) * 4;
         const int* src = nullptr;
         if (pos < feed.it.tok_hi) {
           if (pos < feed.it.main_end) { if (pos < feed.it.limit) src = feed.it.idx + pos; }
@@ -444,85 +471,88 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     }
     cp_async_commit();
   };
-  // Row lane % 8 of block blk as a row number of its pool's 656-byte-pitch view (a cache block may be padded by whole
-  // rows), -1 = invalid; `extra` tells which pool the block's rows live in (a block lies entirely in the main or in the
-  // extra part of the token list: the boundary is a block multiple).
-  auto block_row = [&](const BlockCursor& cu, uint32_t blk, bool& extra) -> int {
-    extra = p.has_extra && cu.it.tok_lo + cu.n * T >= cu.it.main_end;
-    const int64_t total = extra ? p.total_rows2 : p.total_rows;
-    const int page = extra ? p.page2 : p.page, rpb = extra ? p.rows_per_block2 : p.rows_per_block;
-    const int id = (int)lds_u32(ring + ((blk % RING) * PROWS + (lane & 7)) * 4);
-    if (id < 0 || id >= total) return -1;
-    if (rpb == page) return id;
-    const int b = id / page;
-    return b * rpb + (id - b * page);
-  };
-  auto prefetch_block = [&](uint32_t blk) {   // ask L2 for the lines of the warp's rows: lane = 4 row + piece
-    if (!pre.live) return;
-    bool extra;
-    const int vrow = __shfl_sync(0xffffffffu, block_row(pre, blk, extra), lane >> 2);
-    if (vrow >= 0) {
-      const uint8_t* row = (extra ? p.kv_rows2 : p.kv_rows) + (int64_t)vrow * ROW_BYTES;
-      const int piece = lane & 3;            // first / second / last line of the NoPE half, the tail (scales + RoPE half)
-      const uint8_t* a = piece < 3 ? row + 256 * (int)rank + (piece == 2 ? 255 : 128 * piece) : row + ROPE_OFF + 64 * (int)rank + 63;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-      if (piece == 3) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + SCALE_OFF));
-    }
-    pre.advance(p, rec);
-  };
-  auto load_block = [&](uint32_t blk, RowRegs& r) {   // this thread's pieces of block blk; validity bits -> mask ring
-    if (!ldc.live) return;
-    bool extra;
-    const int mine = block_row(ldc, blk, extra);
-    const uint8_t* pool = extra ? p.kv_rows2 : p.kv_rows;
-    const uint32_t bits = __ballot_sync(0xffffffffu, mine >= 0) & 0xffu;
-    if (lane == 0) asm volatile("st.shared.u8 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (blk % RING) + pwarp), "r"(bits) : "memory");
-#pragma unroll
-    for (int it = 0; it < PROWS / 2; ++it) {
-      const int vrow = __shfl_sync(0xffffffffu, mine, 2 * it + (lane >> 4));
-      r.nope[it] = make_uint4(0u, 0u, 0u, 0u);
-      r.scale[it] = 0u;
-      if (vrow >= 0) {
-        const uint8_t* row = pool + (int64_t)vrow * ROW_BYTES;
-        r.nope[it] = ldg_nc_16(row + 256 * (int)rank + 16 * ch);
-        if (p.layout == FMLA_LAYOUT_V32) asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r.scale[it]) : "l"(row + SCALE_OFF + 4 * (2 * (int)rank + (ch >> 3))));
-        else asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(r.scale[it]) : "l"(row + SCALE_OFF + 8 * (int)rank + (ch >> 1)));
-      }
-    }
-    const int vrow = __shfl_sync(0xffffffffu, mine, lane >> 2);
-    r.rope = make_uint4(0u, 0u, 0u, 0u);
-    if (vrow >= 0) r.rope = ldg_nc_16(pool + (int64_t)vrow * ROW_BYTES + ROPE_OFF + 64 * (int)rank + 16 * (lane & 3));
-    ldc.advance(p, rec);
-  };
-
 #pragma unroll 1
   for (int k = 0; k < IDX_LOOKAHEAD; ++k) feed_block(k);
+  const int grp = lane & 3, piece = lane >> 2;
+  for (uint32_t g = 0; g < total_blocks; ++g) {
+    // groups 0 .. g+IDX_LOOKAHEAD-1 are committed; with at most IDX_LOOKAHEAD-1 pending, group g has landed
+    cp_async_wait<IDX_LOOKAHEAD - 1>();
+    __syncwarp();
+    bool extra = false;
+    if (p.has_extra) { uint32_t f; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(f) : "r"(flags + g % RING)); extra = f != 0; }
+    const int64_t total = extra ? p.total_rows2 : p.total_rows;
+    const int page = extra ? p.page2 : p.page, rpb = extra ? p.rows_per_block2 : p.rows_per_block;
+    // row lane % 16 of the warp as a row number of the pool's 656-byte-pitch view (a cache block may be padded by whole rows)
+    const int id = (int)lds_u32(ring + ((g % RING) * GROWS + (lane & 15)) * 4);
+    int vrow = -1;
+    if (id >= 0 && id < total) {
+      if (rpb == page) vrow = id;
+      else { const int b = id / page; vrow = b * rpb + (id - b * page); }
+    }
+    const uint32_t bits = __ballot_sync(0xffffffffu, vrow >= 0) & 0xffffu;
+    int4 rows;
+    rows.x = __shfl_sync(0xffffffffu, vrow, 4 * grp);
+    rows.y = __shfl_sync(0xffffffffu, vrow, 4 * grp + 1);
+    rows.z = __shfl_sync(0xffffffffu, vrow, 4 * grp + 2);
+    rows.w = __shfl_sync(0xffffffffu, vrow, 4 * grp + 3);
+    const int slot = g % NRAW;
+    const uint32_t use = g / NRAW;
+    const bool ok = use == 0 || wait(c, RAW_EMPTY + gw * NRAW + slot, use - 1, 12);
+    if (!__all_sync(0xffffffffu, ok)) return;
+    const uint32_t bar = bar_addr(c, RAW_FULL + gw * NRAW + slot);
+    if (lane == 0) {
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (g % RING) + 2u * gw), "r"(bits) : "memory");
+      mbar_expect_tx(bar, RAW_TX_BYTES);
+    }
+    __syncwarp();
+    const uint32_t dst = c.base + SM_RAW + (uint32_t)slot * RAW_BYTES;
+    const uint32_t q = (uint32_t)(4 * gw + grp);                   // group of four rows within the block
+    if (piece == 0) tma_gather4(dst + RAW_NOPE + q * 1024u, extra ? &p.map_nope2 : &p.map_nope, 256 * (int)rank, rows, bar);
+    else if (piece == 1) tma_gather4(dst + RAW_ROPE + q * ROPE_GROUP, extra ? &p.map_rope2 : &p.map_rope, ROPE_OFF + 64 * (int)rank, rows, bar);
+    else if (piece == 2) tma_gather4(dst + RAW_SCALE + q * SCALE_GROUP, extra ? &p.map_scale2 : &p.map_scale, SCALE_OFF, rows, bar);
+    feed_block(g + IDX_LOOKAHEAD);
+  }
   cp_async_wait<0>();
-  __syncwarp();
-#pragma unroll 1
-  for (int k = 0; k < ROW_PREFETCH; ++k) prefetch_block(k);
-  RowRegs regs;
-  load_block(0, regs);
+}
 
-  for (uint32_t g = 0; cur.live; ++g, cur.advance(p, rec)) {
-    const int st = g % NSTAGE_DECODE;
-    const uint32_t use = g / NSTAGE_DECODE;
-    const uint32_t stage = stage_addr(c, st);
+template <class P>
+__device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank) {
+  const int ptid = threadIdx.x - 32 * NSW, pwarp = ptid >> 5, lane = ptid & 31;
+  const int gw = pwarp / (NPW / NGW);
+  const int ch = lane & 15;
+  uint32_t total_blocks = 0;
+  {
+    Item it;
+    for (int i = 0; get_item(p, rec, i, it); ++i) total_blocks += (uint32_t)num_blocks(it);
+  }
+  for (uint32_t g = 0; g < total_blocks; ++g) {
+    const int st = g % NSTAGE_DECODE, slot = g % NRAW;
+    bool ok = wait(c, RAW_FULL + gw * NRAW + slot, g / NRAW, 14);
+    if (!__all_sync(0xffffffffu, ok)) return;
+    const uint32_t raw = c.base + SM_RAW + (uint32_t)slot * RAW_BYTES, stage = stage_addr(c, st);
+    // all loads first, then the arithmetic, then the stores: the shared-memory accesses are ordered among themselves,
+    // so this order is what lets the four chunks overlap
+    uint4 in[PROWS / 2];
+    uint32_t sc_bits[PROWS / 2];
+#pragma unroll
+    for (int it = 0; it < PROWS / 2; ++it) {
+      const uint32_t row = (uint32_t)PROWS * pwarp + 2 * it + (lane >> 4);
+      const uint32_t sc = raw + RAW_SCALE + (row >> 2) * SCALE_GROUP + (row & 3u) * 16u;
+      in[it] = lds_16(raw + RAW_NOPE + row * 256u + ch * 16u);
+      if (p.layout == FMLA_LAYOUT_V32) sc_bits[it] = lds_u32(sc + 4u * (2u * rank + (ch >> 3)));
+      else asm volatile("ld.shared.u8 %0, [%1];" : "=r"(sc_bits[it]) : "r"(sc + 8u * rank + (ch >> 1)));
+    }
+    const uint32_t rrow = (uint32_t)PROWS * pwarp + (lane >> 2), chr = lane & 3;
+    const uint4 rope = lds_16(raw + RAW_ROPE + (rrow >> 2) * ROPE_GROUP + (rrow & 3u) * 64u + chr * 16u);
     uint4 lo[PROWS / 2], hi[PROWS / 2];
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
-      const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(regs.scale[it]) : e8m0_to_float(regs.scale[it]);
-      dequant_chunk_f16(regs.nope[it], scale_to_half2(scale), lo[it], hi[it]);
+      const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(sc_bits[it]) : e8m0_to_float(sc_bits[it]);
+      dequant_chunk_f16(in[it], scale_to_half2(scale), lo[it], hi[it]);
     }
-    const uint4 rope = regs.rope;
-    // The next block's pieces are requested before the stage wait, so that they travel while this block is stored; the
-    // indices they need were fed IDX_LOOKAHEAD - 1 blocks ago (at most ROW_PREFETCH feeds may still be pending).
-    static_assert(IDX_LOOKAHEAD > ROW_PREFETCH + 1, "the index ring runs ahead of the row prefetch");
-    cp_async_wait<IDX_LOOKAHEAD - 1 - ROW_PREFETCH>();
-    __syncwarp();
-    load_block(g + 1, regs);
     // only the stores need the stage: everything above overlaps the products that still read its previous contents
-    const bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
+    const uint32_t use = g / NSTAGE_DECODE;
+    ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
     if (!__all_sync(0xffffffffu, ok)) return;
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
@@ -531,18 +561,16 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       st_shared16(panel + swz(row, 2 * (ch & 3)), lo[it]);
       st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi[it]);
     }
-    {
-      const uint32_t row = (uint32_t)PROWS * pwarp + (lane >> 2), chr = lane & 3;
-      st_shared16(stage + ROPE_PANEL + row * 64u + ((chr ^ ((row >> 1) & 3u)) << 4), rope);
-    }
-    // the dequantised rows (generic proxy) become visible to the MMAs
+    st_shared16(stage + ROPE_PANEL + rrow * 64u + ((chr ^ ((rrow >> 1) & 3u)) << 4), rope);
+    // the dequantised rows (generic proxy) become visible to the MMAs, and this warp's reads of the raw slot
+    // are ordered before the TMA writes of the slot's next use
     fence_async_smem();
     __syncwarp();
-    if (lane == 0) arrive_leader(c, KV_FULL + st);
-    prefetch_block(g + ROW_PREFETCH);
-    feed_block(g + IDX_LOOKAHEAD);
+    if (lane == 0) {
+      mbar_arrive(bar_addr(c, RAW_EMPTY + gw * NRAW + slot));
+      arrive_leader(c, KV_FULL + st);
+    }
   }
-  cp_async_wait<0>();
 }
 
 // ---- MMA issuers (one thread each, CTA 0) ---------------------------------------------------------
@@ -1010,7 +1038,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
 
 // ---- kernel ------------------------------------------------------------------------------------------
 template <int MODE, int EXTRA>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(MODE), 1)
 pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Ctx c;
@@ -1035,6 +1063,10 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
     for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(bar_addr(c, KV_FULL + s), 2 * NPW);    // the producer warps of both CTAs
       mbar_init(bar_addr(c, KV_EMPTY + s), 1);
+    }
+    for (int s = 0; s < NGW * NRAW; ++s) {
+      mbar_init(bar_addr(c, RAW_FULL + s), 1);               // the gather warp's expect_tx arrival + the bytes
+      mbar_init(bar_addr(c, RAW_EMPTY + s), NPW / NGW);      // the converter warps that read this quarter of the slot
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_addr(c, S_FULL + b), 1);
@@ -1062,17 +1094,18 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
     reg_inc<REGS_SOFTMAX>();
     softmax_role(p, rec, c, tmem, rank);
   } else if (warp < NSW + NPW) {
-    reg_dec<REGS_PRODUCER>();
+    reg_dec<regs_producer(MODE)>();
     if (p.mode == 0) convert_role(p, rec, c, rank);
     else producer_role(p, rec, c, rank);
-  } else {
-    reg_dec<REGS_ISSUER>();
-    if (warp < GATHER_WARP) {
-      if (rank == 0 && (threadIdx.x & 31) == 0) {
-        if (warp < PV_WARP) issue_qk(p, rec, c, tmem, (uint32_t)(warp - QK_WARP));
-        else issue_pv(p, rec, c, tmem);
-      }
+  } else if (warp < GATHER_WARP) {
+    reg_dec<regs_issuer(MODE)>();
+    if (rank == 0 && (threadIdx.x & 31) == 0) {
+      if (warp < PV_WARP) issue_qk(p, rec, c, tmem, (uint32_t)(warp - QK_WARP));
+      else if (warp == PV_WARP) issue_pv(p, rec, c, tmem);
     }
+  } else {
+    reg_dec<REGS_GATHER>();
+    if (p.mode == 0) gather_role(p, rec, c, rank, warp - GATHER_WARP);
   }
 
   tc_fence_before_sync();
@@ -1138,7 +1171,7 @@ static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
   static_cast<Params&>(pt) = p;
   // FMLA_DISABLE_Q_TMA=1 forces the plain-load Q path, which otherwise only runs when the driver refuses q's strides
   if (const char* e = std::getenv("FMLA_DISABLE_Q_TMA")) if (e[0] == '1') pt.q_tma = 0;
-  pair_attn_kernel<MODE, EXTRA><<<grid, THREADS, SMEM_BYTES, stream>>>(pt);
+  pair_attn_kernel<MODE, EXTRA><<<grid, threads_of(MODE), SMEM_BYTES, stream>>>(pt);
   FMLA_CUDA(cudaGetLastError());
   return FMLA_OK;
 }
@@ -1205,7 +1238,16 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
                "sparse_decode: the tensor-core kernel needs KV block strides that are multiples of 656 bytes and at most 2^31 rows "
                "per cache (got strides %lld / %lld)", (long long)a.kv_stride_block, (long long)a.extra_kv_stride_block);
   p.rows_per_block = (int)(a.kv_stride_block / ROW_BYTES);
+  const uint64_t vrows = (uint64_t)(a.num_blocks - 1) * p.rows_per_block + a.page_block_size;
+  if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows, ROW_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+  if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows, ROW_BYTES, 64, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+  if (int rc = tc::make_row_map(&p.map_scale, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows, ROW_BYTES, 16, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+  p.map_nope2 = p.map_nope; p.map_rope2 = p.map_rope; p.map_scale2 = p.map_scale;      // replaced below when there is an extra cache
   if (a.extra_kv != nullptr) {
+    const uint64_t vrows2 = (uint64_t)(a.extra_num_blocks - 1) * (uint64_t)(a.extra_kv_stride_block / ROW_BYTES) + a.extra_page_block_size;
+    if (int rc = tc::make_row_map(&p.map_nope2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows2, ROW_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    if (int rc = tc::make_row_map(&p.map_rope2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows2, ROW_BYTES, 64, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    if (int rc = tc::make_row_map(&p.map_scale2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows2, ROW_BYTES, 16, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
     p.has_extra = 1;
     p.kv_rows2 = reinterpret_cast<const uint8_t*>(a.extra_kv);
     p.rows_per_block2 = (int)(a.extra_kv_stride_block / ROW_BYTES);
