@@ -18,6 +18,8 @@ LAYOUT_V32, LAYOUT_MXFP8 = 0, 1
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
 SCHED_META_INTS = 8
 STATIC_SCRATCH_ROWS = 16384
+OPTION_PLAIN_Q_LOADS = 1
+STATUS_CLIPPED = 100
 
 _i32p = C.POINTER(C.c_int32)
 _f32p = C.POINTER(C.c_float)
@@ -94,6 +96,8 @@ class CacheIndexArgs(C.Structure):
 EXPORTS = {
     "fmla_version": (C.c_int, []),
     "fmla_last_error": (C.c_char_p, []),
+    "fmla_set_option": (C.c_int, [C.c_int, C.c_int]),
+    "fmla_tensor_map_cache_stats": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "fmla_decode_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p]),
     "fmla_sched_meta": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
     "fmla_sparse_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),

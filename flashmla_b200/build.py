@@ -73,5 +73,21 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_test_helper(force: bool = False) -> str:
+    """Compiles tests/wait_timeout/wait_timeout.cu (a test-only kernel whose bounded wait runs out) into a shared
+    object beside its source, so that the GPU test finds it prebuilt."""
+    src = os.path.join(ROOT, "tests", "wait_timeout", "wait_timeout.cu")
+    out = os.path.join(ROOT, "tests", "wait_timeout", "libwait_timeout.so")
+    newest = max(os.path.getmtime(src), os.path.getmtime(os.path.join(CSRC, "sm100_ptx.cuh")))
+    if force or not os.path.exists(out) or os.path.getmtime(out) < newest:
+        r = subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-lineinfo",
+                            "-Xcompiler", "-fPIC", "-shared", "-o", out, src], capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("nvcc failed on the wait_timeout test helper")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_test_helper(force="--force" in sys.argv))

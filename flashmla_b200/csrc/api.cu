@@ -66,7 +66,7 @@ using namespace fmla;
 
 extern "C" {
 
-int fmla_version(void) { return 120; }   // 120: backward workspace/status fields and fmla_sparse_prefill_bwd_workspace (tensor-core backward)
+int fmla_version(void) { return 130; }   // 130: fmla_set_option, fmla_tensor_map_cache_stats, FMLA_STATUS_* codes
 
 const char* fmla_last_error(void) { return g_error; }
 
@@ -207,6 +207,20 @@ int fmla_sparse_prefill_bwd(const FmlaPrefillBwdArgs* a, void* cuda_stream) {
   const bool use_tc = a->kernel == FMLA_KERNEL_TC || (a->kernel != FMLA_KERNEL_SIMT && tc_ok && a->workspace != nullptr);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   return use_tc ? launch_tc_prefill_bwd(*a, stream) : launch_simt_prefill_bwd(*a, stream);
+}
+
+int fmla_set_option(int option, int value) {
+  if (option == FMLA_OPTION_PLAIN_Q_LOADS) { tc_set_plain_q_loads(value); return FMLA_OK; }
+  set_error("set_option: unknown option %d", option);
+  return FMLA_ERR_INVALID_ARG;
+}
+
+int fmla_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses) {
+  FMLA_REQUIRE(hits && misses, FMLA_ERR_INVALID_ARG, "tensor_map_cache_stats: null output pointer");
+  unsigned long long h = 0, m = 0;
+  tc_map_cache_stats(&h, &m);
+  *hits = h; *misses = m;
+  return FMLA_OK;
 }
 
 int64_t fmla_sparse_prefill_bwd_workspace(int s_q, int h_q, int topk, int kernel) {

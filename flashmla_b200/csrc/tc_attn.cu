@@ -50,11 +50,12 @@
 // (csrc/sm100/prefill/sparse/common_subroutine.h:186-206).
 #include <cuda.h>
 
-#include <cstdlib>
+#include <atomic>
 #include <math_constants.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace fmla {
 namespace tc {
@@ -340,9 +341,10 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
-// fp32 scale -> packed half2 scale, clamped to [0, 2^7]
+// fp32 scale -> packed half2 scale, clamped to [0, 2^7]: e4m3 times a larger scale can leave fp16's range
+constexpr float MAX_STAGED_SCALE = 128.f;
 __device__ __forceinline__ uint32_t scale_to_half2(float scale) {
-  const __half h = __float2half_rn(fminf(scale, 128.f));
+  const __half h = __float2half_rn(fminf(scale, MAX_STAGED_SCALE));
   const uint32_t u = (uint32_t)__half_as_ushort(h);
   return u | (u << 16);
 }
@@ -525,6 +527,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     Item it;
     for (int i = 0; get_item(p, rec, i, it); ++i) total_blocks += (uint32_t)num_blocks(it);
   }
+  bool clipped = false;      // a scale beyond what the fp16 stage can hold was met (the values were clipped)
   for (uint32_t g = 0; g < total_blocks; ++g) {
     const int st = g % NSTAGE_DECODE, slot = g % NRAW;
     bool ok = wait(c, RAW_FULL + gw * NRAW + slot, g / NRAW, 14);
@@ -548,6 +551,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
       const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(sc_bits[it]) : e8m0_to_float(sc_bits[it]);
+      clipped |= scale > MAX_STAGED_SCALE;
       dequant_chunk_f16(in[it], scale_to_half2(scale), lo[it], hi[it]);
     }
     // only the stores need the stage: everything above overlaps the products that still read its previous contents
@@ -571,6 +575,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       arrive_leader(c, KV_FULL + st);
     }
   }
+  if (__any_sync(0xffffffffu, clipped) && lane == 0 && c.status) atomicCAS(c.status, 0, FMLA_STATUS_CLIPPED);
 }
 
 // ---- MMA issuers (one thread each, CTA 0) ---------------------------------------------------------
@@ -673,6 +678,14 @@ __device__ __noinline__ void leave_group(uint32_t leave_word, int warp) {
   }
 }
 
+// running maximum of |x| over packed bf16 pairs
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(acc), "r"(v));
+  return r;
+}
+// whether a packed pair of non-negative bf16 holds a value beyond fp16's largest (65504; the next bf16 is 65536 = 0x4780)
+__device__ __forceinline__ bool beyond_f16(uint32_t absmax) { return (((absmax & 0x7fff7fffu) + 0x38803880u) & 0x80008000u) != 0u; }
 // bf16 pair -> fp16 pair (values beyond fp16's range saturate to +-65504)
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
   uint32_t r;
@@ -689,7 +702,7 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 // Column group g of a lane loads NoPE columns 64g .. 64g+63; the thread also writes RoPE dims 32 half + 16 g .. + 15
 // of its head into the 128B-swizzled RoPE panel.
 template <class P>
-__device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head, int h, int half, int g) {
+__device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head, int h, int half, int g, uint32_t& qmax) {
   const __nv_bfloat16* row = it.q + (int64_t)head * p.q_stride_h;
   const __nv_bfloat16* nope = row + 256 * half + 128 * g;
   const __nv_bfloat16* rope = row + 512 + 32 * half + 16 * g;
@@ -711,14 +724,14 @@ __device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const I
   for (int k = 0; k < 8; ++k) { r[4 * k] = a[k].x; r[4 * k + 1] = a[k].y; r[4 * k + 2] = a[k].z; r[4 * k + 3] = a[k].w; }
   if (p.mode == 0) {   // decode multiplies the NoPE part in fp16
 #pragma unroll
-    for (int k = 0; k < 32; ++k) r[k] = bf16x2_to_f16x2(r[k]);
+    for (int k = 0; k < 32; ++k) { qmax = absmax_bf16x2(qmax, r[k]); r[k] = bf16x2_to_f16x2(r[k]); }
   }
   tmem_st32(tmem_lane + TM_Q + 64 * g, r);
 #pragma unroll
   for (int k = 0; k < 8; ++k) { r[4 * k] = b[k].x; r[4 * k + 1] = b[k].y; r[4 * k + 2] = b[k].z; r[4 * k + 3] = b[k].w; }
   if (p.mode == 0) {
 #pragma unroll
-    for (int k = 0; k < 32; ++k) r[k] = bf16x2_to_f16x2(r[k]);
+    for (int k = 0; k < 32; ++k) { qmax = absmax_bf16x2(qmax, r[k]); r[k] = bf16x2_to_f16x2(r[k]); }
   }
   tmem_st32(tmem_lane + TM_Q + 64 * g + 32, r);
   st_shared16(c.base + SM_QROPE + swz(h, 4 * half + 2 * g), e[0]);
@@ -744,7 +757,7 @@ __device__ __forceinline__ void half_sync(int half) { asm volatile("bar.sync %0,
 // has been copied: the caller uses them to run the previous item's epilogue in the shadow of the tiles' latency.
 template <class P, class Pre, class Post>
 __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head0, int h, int half,
-                                           int g, bool issuer, uint32_t& uses, uint32_t& items, Pre pre, Post post) {
+                                           int g, bool issuer, uint32_t& uses, uint32_t& items, uint32_t& qmax, Pre pre, Post post) {
   const uint32_t buf = c.base + SM_XCHG + 8192u * half;
   const uint32_t bar = bar_addr(c, QT_FULL + half), bar_rope = bar_addr(c, QR_FULL);
   const int c2 = p.mode == 0 ? it.sq : it.req, c3 = p.mode == 0 ? it.req : 0;
@@ -780,7 +793,7 @@ __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item&
     if (issuer && r < 3) request(r + 1);
     if (p.mode == 0) {   // decode multiplies the NoPE part in fp16
 #pragma unroll
-      for (int k = 0; k < 16; ++k) v[k] = bf16x2_to_f16x2(v[k]);
+      for (int k = 0; k < 16; ++k) { qmax = absmax_bf16x2(qmax, v[k]); v[k] = bf16x2_to_f16x2(v[k]); }
     }
     tmem_st16(tmem_lane + TM_Q + 32 * r + 16 * g, v);
     post(r);
@@ -829,11 +842,12 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   const int head0 = blockIdx.z * 128 + (int)rank * 64;
   const bool q_issuer = h == 0 && g == 0;
   uint32_t qt_uses = 0, qr_items = 0;
+  uint32_t q_absmax = 0;                     // decode: largest |q| of the NoPE part seen by this thread (Q is staged in fp16)
   if (have) {
     if (p.q_tma) {
-      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
+      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
     } else {
-      load_q_to_tmem(p, c, it, tmem_lane, head, h, half, g);
+      load_q_to_tmem(p, c, it, tmem_lane, head, h, half, g, q_absmax);
     }
     tc_fence_before_sync();
     __syncwarp();
@@ -1013,14 +1027,14 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     // With the TMA path the epilogue's four chunks run between the Q tiles, in the shadow of their latency;
     // either way the next item's first QK^T overlaps the rest of the epilogue.
     if (have_next && p.q_tma) {
-      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
+      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(c, Q_FULL);
     } else {
       asm volatile("bar.sync 9, 256;" ::: "memory");
       if (have_next) {
-        load_q_to_tmem(p, c, it_next, tmem_lane, head, h, half, g);
+        load_q_to_tmem(p, c, it_next, tmem_lane, head, h, half, g, q_absmax);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) arrive_leader(c, Q_FULL);
@@ -1034,6 +1048,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     it = it_next;
     have = have_next;
   }
+  if (p.mode == 0 && __any_sync(0xffffffffu, beyond_f16(q_absmax)) && lane == 0 && c.status) atomicCAS(c.status, 0, FMLA_STATUS_CLIPPED);
 }
 
 // ---- kernel ------------------------------------------------------------------------------------------
@@ -1114,63 +1129,41 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
   if (warp == QK_WARP) tmem_dealloc<2>(tmem, TM_COLS);
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point table (no direct libcuda dependency).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// 2-D map over `rows` rows of `cols` elements with a row pitch of `pitch_bytes`; one box is `box_cols` elements of one row.
 // q viewed as (576, h_q, n1, n2) with element strides; box = box_cols dims x 64 heads.  Returns false if the driver
 // refuses the strides (the kernel then reads Q with plain loads).
 static bool make_q_map(CUtensorMap* map, const void* q, int h_q, uint64_t n1, uint64_t n2, int64_t stride_h, int64_t stride1,
                        int64_t stride2, uint32_t box_cols, CUtensorMapSwizzle swizzle) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr || stride_h <= 0 || stride1 <= 0 || stride2 <= 0) return false;
-  const cuuint64_t dims[4] = {576, (cuuint64_t)h_q, n1, n2};
-  const cuuint64_t strides[3] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride1 * 2, (cuuint64_t)stride2 * 2};
-  const cuuint32_t box[4] = {box_cols, 64, 1, 1};
-  const cuuint32_t elem[4] = {1, 1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (stride_h <= 0 || stride1 <= 0 || stride2 <= 0) return false;
+  const uint64_t dims[4] = {576, (uint64_t)h_q, n1, n2};
+  const uint64_t strides[3] = {(uint64_t)stride_h * 2, (uint64_t)stride1 * 2, (uint64_t)stride2 * 2};
+  const uint32_t box[4] = {box_cols, 64, 1, 1};
+  return tmap::encode(map, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, swizzle) == 0;
 }
+// 2-D map over `rows` rows of `cols` elements with a row pitch of `pitch_bytes`; one box is `box_cols` elements of one row.
 static int make_row_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, uint64_t cols, uint64_t rows,
                         uint64_t pitch_bytes, uint32_t box_cols, CUtensorMapSwizzle swizzle) {
-  EncodeTiledFn fn = encode_fn();
-  FMLA_REQUIRE(fn != nullptr, FMLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {pitch_bytes};
-  const cuuint32_t box[2] = {box_cols, 1};
-  const cuuint32_t elem[2] = {1, 1};
-  const CUresult rc = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  FMLA_REQUIRE(rc == CUDA_SUCCESS, FMLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with driver error %d", (int)rc);
+  const uint64_t dims[2] = {cols, rows};
+  const uint64_t strides[1] = {pitch_bytes};
+  const uint32_t box[2] = {box_cols, 1};
+  const int rc = tmap::encode(map, base, dt, 2, dims, strides, box, swizzle);
+  FMLA_REQUIRE(rc >= 0, FMLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  FMLA_REQUIRE(rc == 0, FMLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with driver error %d", rc);
   return FMLA_OK;
 }
 
+// Diagnostic switch (fmla_set_option): read Q with plain loads even when a tensor map could be made, the path that
+// otherwise only runs when the driver refuses q's strides.
+std::atomic<int> g_plain_q_loads{0};
+
 template <int MODE, int EXTRA>
 static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
-  static bool attr_set[64] = {};
-  int dev = 0;
-  FMLA_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    FMLA_CUDA(cudaFuncSetAttribute(pair_attn_kernel<MODE, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    attr_set[dev] = true;
-  }
+  static tmap::PerDeviceOnce once;
+  FMLA_CUDA(once.run([] {
+    return cudaFuncSetAttribute(pair_attn_kernel<MODE, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  }));
   ParamsT<MODE, EXTRA> pt;
   static_cast<Params&>(pt) = p;
-  // FMLA_DISABLE_Q_TMA=1 forces the plain-load Q path, which otherwise only runs when the driver refuses q's strides
-  if (const char* e = std::getenv("FMLA_DISABLE_Q_TMA")) if (e[0] == '1') pt.q_tma = 0;
+  if (g_plain_q_loads.load(std::memory_order_relaxed)) pt.q_tma = 0;
   pair_attn_kernel<MODE, EXTRA><<<grid, threads_of(MODE), SMEM_BYTES, stream>>>(pt);
   FMLA_CUDA(cudaGetLastError());
   return FMLA_OK;
@@ -1182,6 +1175,13 @@ static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
 
 }  // namespace tc
 
+
+void tc_set_plain_q_loads(int on) { tc::g_plain_q_loads.store(on ? 1 : 0, std::memory_order_relaxed); }
+void tc_map_cache_stats(unsigned long long* hits, unsigned long long* misses) {
+  tmap::Cache& c = tmap::cache();
+  std::lock_guard<std::mutex> lock(c.mu);
+  *hits = c.hits; *misses = c.misses;
+}
 
 bool tc_supported(int h_q) { return h_q > 0 && h_q % 64 == 0; }   // 64 (mod 128): the last pair runs half empty
 

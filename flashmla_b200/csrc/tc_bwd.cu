@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace fmla {
 namespace bwd {
@@ -592,30 +593,12 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16*
 }
 
 // ---- host -------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
 // bf16 tensor of `rank` dims (innermost first) with byte strides for dims 1.., 128-byte swizzled boxes.
-static int make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-                    const cuuint32_t* box, const char* what) {
-  EncodeTiledFn fn = encode_fn();
-  FMLA_REQUIRE(fn != nullptr, FMLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint32_t elem[3] = {1, 1, 1};
-  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, elem,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  FMLA_REQUIRE(rc == CUDA_SUCCESS, FMLA_ERR_CUDA, "sparse_prefill_bwd: cuTensorMapEncodeTiled failed for %s with driver error %d", what, (int)rc);
+static int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                    const uint32_t* box, const char* what) {
+  const int rc = tmap::encode(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  FMLA_REQUIRE(rc >= 0, FMLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  FMLA_REQUIRE(rc == 0, FMLA_ERR_CUDA, "sparse_prefill_bwd: cuTensorMapEncodeTiled failed for %s with driver error %d", what, rc);
   return FMLA_OK;
 }
 
@@ -644,29 +627,29 @@ int launch_tc_prefill_bwd(const FmlaPrefillBwdArgs& a, cudaStream_t stream) {
 
   Params p{};
   {
-    const cuuint64_t dims[3] = {(cuuint64_t)D_QK, (cuuint64_t)a.h_q, (cuuint64_t)a.s_q};
-    const cuuint64_t strides[2] = {(cuuint64_t)a.q_stride_h * 2, (cuuint64_t)a.q_stride_s * 2};
-    const cuuint32_t box[3] = {64, HG, 1};
+    const uint64_t dims[3] = {(cuuint64_t)D_QK, (cuuint64_t)a.h_q, (cuuint64_t)a.s_q};
+    const uint64_t strides[2] = {(cuuint64_t)a.q_stride_h * 2, (cuuint64_t)a.q_stride_s * 2};
+    const uint32_t box[3] = {64, HG, 1};
     if (int rc = make_map(&p.map_q, a.q, 3, dims, strides, box, "q")) return rc;
   }
   {
-    const cuuint64_t dims[3] = {(cuuint64_t)D_V, (cuuint64_t)a.h_q, (cuuint64_t)a.s_q};
-    const cuuint64_t strides[2] = {(cuuint64_t)a.do_stride_h * 2, (cuuint64_t)a.do_stride_s * 2};
-    const cuuint32_t box[3] = {64, HG, 1};
+    const uint64_t dims[3] = {(cuuint64_t)D_V, (cuuint64_t)a.h_q, (cuuint64_t)a.s_q};
+    const uint64_t strides[2] = {(cuuint64_t)a.do_stride_h * 2, (cuuint64_t)a.do_stride_s * 2};
+    const uint32_t box[3] = {64, HG, 1};
     if (int rc = make_map(&p.map_do, a.dout, 3, dims, strides, box, "dout")) return rc;
   }
   {
-    const cuuint64_t dims[2] = {(cuuint64_t)D_QK, (cuuint64_t)a.s_kv};
-    const cuuint64_t strides[1] = {(cuuint64_t)a.kv_stride_s * 2};
-    const cuuint32_t box[2] = {64, 1};
+    const uint64_t dims[2] = {(cuuint64_t)D_QK, (cuuint64_t)a.s_kv};
+    const uint64_t strides[1] = {(cuuint64_t)a.kv_stride_s * 2};
+    const uint32_t box[2] = {64, 1};
     if (int rc = make_map(&p.map_kv, a.kv, 2, dims, strides, box, "kv")) return rc;
   }
   __nv_bfloat16* ws_p = static_cast<__nv_bfloat16*>(a.workspace);
   __nv_bfloat16* ws_ds = ws_p + chunk * HG * topk_pad;
   {
-    const cuuint64_t dims[2] = {(cuuint64_t)topk_pad, (cuuint64_t)(chunk * HG)};
-    const cuuint64_t strides[1] = {(cuuint64_t)topk_pad * 2};
-    const cuuint32_t box[2] = {64, HG};
+    const uint64_t dims[2] = {(cuuint64_t)topk_pad, (cuuint64_t)(chunk * HG)};
+    const uint64_t strides[1] = {(cuuint64_t)topk_pad * 2};
+    const uint32_t box[2] = {64, HG};
     if (int rc = make_map(&p.map_p, ws_p, 2, dims, strides, box, "workspace")) return rc;
     if (int rc = make_map(&p.map_ds, ws_ds, 2, dims, strides, box, "workspace")) return rc;
   }
@@ -679,8 +662,11 @@ int launch_tc_prefill_bwd(const FmlaPrefillBwdArgs& a, cudaStream_t stream) {
   p.groups = groups; p.h_q = a.h_q; p.s_kv = a.s_kv; p.topk = a.topk; p.topk_pad = topk_pad;
   p.sm_scale = a.sm_scale; p.status = a.status;
 
-  FMLA_CUDA(cudaFuncSetAttribute(bwd_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sc::SMEM));
-  FMLA_CUDA(cudaFuncSetAttribute(bwd_dq_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GRAD_SMEM));
+  static tmap::PerDeviceOnce once;
+  FMLA_CUDA(once.run([] {
+    const cudaError_t e = cudaFuncSetAttribute(bwd_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sc::SMEM);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(bwd_dq_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GRAD_SMEM);
+  }));
   FMLA_CUDA(cudaMemsetAsync(a.dkv_accum, 0, sizeof(float) * (size_t)a.s_kv * D_QK, stream));
   for (int64_t u0 = 0; u0 < units; u0 += chunk) {
     const unsigned n = (unsigned)std::min<int64_t>(chunk, units - u0);

@@ -4,7 +4,8 @@
  * Every entry point takes plain pointers and sizes, enqueues work on the given CUDA stream
  * and returns immediately (no stream synchronisation, no device allocation, no frees).
  * All device buffers — inputs, outputs, scheduler metadata and split-KV scratch — are owned
- * by the caller and must stay valid until the enqueued work has run.  Return value 0 means
+ * by the caller and must stay valid until the enqueued work has run; the one exception is
+ * fmla_sparse_decode_static_scratch, whose split-KV scratch is an array inside the library.  Return value 0 means
  * success; any other value is one of the FMLA_ERR_* codes and fmla_last_error() returns a
  * thread-local, human readable description.  Nothing here calls exit() or traps the device.
  *
@@ -28,6 +29,19 @@ extern "C" {
 #define FMLA_ERR_ARCH         5   /* device is not compute capability 10.x */
 #define FMLA_ERR_TIMEOUT      6   /* a bounded device-side wait gave up (reported through a status word) */
 
+/*
+ * Values of the optional device status word (FmlaDecodeArgs.status and its siblings), which starts at 0 and keeps the
+ * first non-zero value written to it:
+ *   1 .. 99             a kernel gave up a bounded wait (the number names the wait); the call's results are invalid.
+ *   FMLA_STATUS_CLIPPED  the tensor-core decode kernel stages the dequantised NoPE part and Q in fp16 and met a value
+ *                       outside that range: a cache scale above 2^7 (a row whose tile maximum exceeds 57344) or a
+ *                       |q| above 65504.  Such values were clipped, so the call's results are not to be trusted; run
+ *                       the call again with FMLA_KERNEL_SIMT, which multiplies in fp32 like the reference
+ *                       (tests/quant.py:93-104).  FMLA_KERNEL_AUTO cannot know the values in advance and picks the
+ *                       tensor-core kernel whenever the shape allows.
+ */
+#define FMLA_STATUS_CLIPPED 100
+
 /* KV-cache row layouts, 656 bytes per token, d_qk = 576 (512 NoPE + 64 RoPE), one KV head. */
 #define FMLA_LAYOUT_V32    0   /* 512 e4m3 | 4 x fp32 scale (per 128) | 64 bf16   (flash_mla/flash_mla_interface.py:94-98) */
 #define FMLA_LAYOUT_MXFP8  1   /* 512 e4m3 | 16 x e8m0 scale (per 32) | 64 bf16   (no counterpart in the reference) */
@@ -45,6 +59,20 @@ extern "C" {
 
 int fmla_version(void);
 const char* fmla_last_error(void);
+
+/*
+ * Process-wide switches, for diagnosis and tests.  No counterpart in the reference.
+ *   FMLA_OPTION_PLAIN_Q_LOADS  non-zero: the tensor-core attention kernel reads Q with plain loads instead of TMA
+ *                              tiles (the path it otherwise takes only when the driver refuses q's strides).
+ */
+#define FMLA_OPTION_PLAIN_Q_LOADS 1
+int fmla_set_option(int option, int value);
+
+/*
+ * Hits and misses of the library's table of encoded TMA descriptors.  The reference encodes its descriptors on every
+ * call (csrc/sm100/decode/head64/kernel.cuh:913-930); here a call whose buffers and shapes were seen before encodes none.
+ */
+int fmla_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses);
 
 /*
  * Split-KV plan for a decode shape on `device`: how many SM partitions the decode kernel is
@@ -127,6 +155,8 @@ int fmla_sparse_decode(const FmlaDecodeArgs* args, void* cuda_stream);
  *   limit     (b + num_sm_parts) * s_q * h_q <= FMLA_STATIC_SCRATCH_ROWS, else FMLA_ERR_UNSUPPORTED.
  *   set-up    the first call on a device looks the array's address up (which may load the module on that
  *             device); make that call before any stream capture.  Later calls only launch the two kernels.
+ *             The address is kept for the life of the process: after a cudaDeviceReset of that device (which
+ *             unloads the module) it is stale and this entry point must not be used on it again.
  *   sharing   one array per device: calls on one device that may overlap in time (different streams
  *             or host threads) race on it, so order them on one stream or by events.  The array keeps the
  *             last call's contents; nothing in it needs clearing between calls.

@@ -148,18 +148,98 @@ def test_both_kernel_families_agree_with_oracle(monkeypatch, kernel, h_q):
     check_prefill(o, mx, l, ro, rm, rl, strict=True)
 
 
-def test_plain_load_q_path(monkeypatch):
+def test_plain_load_q_path():
     """Q normally reaches tensor memory through TMA tiles; the plain-load path (taken when the driver refuses q's
-    strides for a tensor map) is forced here and must give the same bits."""
+    strides for a tensor map) is forced here through fmla_set_option and must give the same bits."""
+    lib = _lib.load()
     w = wl.make_decode_workload(4, 2, 128, 512, 600, 2500, seed=77, invalid_frac=0.05, with_sink=True, **REFD)
-    out0, lse0, _ = run_decode(w)
-    monkeypatch.setenv("FMLA_DISABLE_Q_TMA", "1")
-    out1, lse1, _ = run_decode(w)
-    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
     from gpu_utils import run_prefill
     pw = wl.make_prefill_workload(150, 900, 128, 256, seed=78, std=0.1, sm_scale=0.5)
-    monkeypatch.delenv("FMLA_DISABLE_Q_TMA")
+    out0, lse0, _ = run_decode(w)
     ref = run_prefill(pw)
-    monkeypatch.setenv("FMLA_DISABLE_Q_TMA", "1")
-    got = run_prefill(pw)
+    try:
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_Q_LOADS, 1))
+        out1, lse1, _ = run_decode(w)
+        got = run_prefill(pw)
+    finally:
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_Q_LOADS, 0))
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
     assert all(torch.equal(a, b) for a, b in zip(ref, got))
+
+
+def _raw_decode(w, kernel=None, monkeypatch=None):
+    """flash_mla_with_kvcache without the helper's status assertion; returns (out, lse, status)."""
+    import flashmla_b200
+    if kernel is not None:
+        monkeypatch.setenv("FMLA_KERNEL", kernel)
+    out, lse = flash_mla.flash_mla_with_kvcache(cu(w.q), cu(w.kv_rows), None, None, 512, flash_mla.get_mla_metadata()[0], None,
+                                                w.sm_scale, False, True, cu(w.indices), kvcache_layout=w.layout)
+    status = flashmla_b200.kernel_status(DEV)
+    if kernel is not None:
+        monkeypatch.delenv("FMLA_KERNEL")
+    return out, lse, status
+
+
+@pytest.mark.parametrize("layout", [wl.LAYOUT_V32, wl.LAYOUT_MXFP8])
+def test_cache_values_beyond_the_fp16_stage_are_reported_not_silently_clipped(layout, monkeypatch):
+    """The tensor-core decode kernel stages dequantised values in fp16.  Tile scales up to 2^7 (tile maxima up to
+    57344) are exact; beyond that it reports FMLA_STATUS_CLIPPED through the status word, and the CUDA-core kernel,
+    which multiplies in fp32 like the reference (tests/quant.py:93-104), gives the right answer."""
+    kw = dict(seed=51, invalid_frac=0.02, q_std=1e-4, layout=layout)
+    # tile maxima between 2^14 and 5e4: the largest scale is exactly 2^7, nothing is clipped
+    w = wl.make_decode_workload(3, 2, 128, 256, 300, 900, kv_std=2e4, clamp=5e4, **kw)
+    out, lse, status = _raw_decode(w)
+    assert status == 0
+    ref_out, ref_lse = oracle_decode(w)
+    check_decode(out, lse, ref_out, ref_lse, strict=False)
+    # tile maxima around 1e5: scales of 2^8, beyond the fp16 stage
+    w = wl.make_decode_workload(3, 2, 128, 256, 300, 900, kv_std=4e4, **kw)
+    _, _, status = _raw_decode(w)
+    assert status == _lib.STATUS_CLIPPED
+    out, lse, status = _raw_decode(w, "simt", monkeypatch)
+    assert status == 0
+    ref_out, ref_lse = oracle_decode(w)
+    check_decode(out, lse, ref_out, ref_lse, strict=False)
+
+
+def test_queries_beyond_the_fp16_stage_are_reported():
+    w = wl.make_decode_workload(2, 1, 128, 128, 200, 400, seed=52, q_std=1.0, kv_std=0.1, clamp=1.0)
+    w.q[1, 0, 5, 17] = 7e4            # representable in bf16, not in fp16
+    _, _, status = _raw_decode(w)
+    assert status == _lib.STATUS_CLIPPED
+
+
+def test_v32_scales_that_are_not_powers_of_two():
+    """The V32 format stores fp32 scales; the quantiser only emits powers of two, but any scale is legal
+    (tests/quant.py:101-104 multiplies by whatever is stored).  e4m3 times 1.5 * 2^k is still exact in fp16."""
+    w = wl.make_decode_workload(3, 2, 128, 256, 300, 900, seed=53, invalid_frac=0.02, **REFD)
+    rows = w.kv_rows.view(-1, 656)
+    scales = rows[:, 512:528].contiguous().view(torch.float32)
+    rows[:, 512:528] = (scales * 1.5).view(torch.uint8)
+    out, lse, _ = run_decode(w)
+    ref_out, ref_lse = oracle_decode(w)
+    check_decode(out, lse, ref_out, ref_lse)
+
+
+def test_unsplit_batch_is_complete_for_the_next_kernel_in_the_stream():
+    """A batch in which no request is split leaves the combine kernel nothing to merge; its blocks must still wait for
+    the attention kernel, or the next kernel in the stream (here a copy of `out`, launched without any host
+    synchronisation) could read results that are not written yet."""
+    lib = _lib.load()
+    parts, ovh, blk = C.c_int32(), C.c_int32(), C.c_int32()
+    _lib.check(lib.fmla_decode_plan(0, 128, 1, _lib.KERNEL_AUTO, C.byref(parts), C.byref(ovh), C.byref(blk)))
+    b = parts.value                       # one whole request per partition: nothing is split
+    w = wl.make_decode_workload(b, 1, 128, 2048, 2100, 2100, seed=54, **REFD)
+    q, kv, idx = cu(w.q), cu(w.kv_rows), cu(w.indices)
+    sched = flash_mla.get_mla_metadata()[0]
+    ref, ref_lse = flash_mla.flash_mla_with_kvcache(q, kv, None, None, 512, sched, None, w.sm_scale, False, True, idx)
+    torch.cuda.synchronize()
+    splits = sched.num_splits.cpu()
+    assert int((splits[1:] - splits[:-1]).max()) == 1, "the case is meant to have no split request"
+    ref = ref.clone()
+    for _ in range(20):
+        out, lse = flash_mla.flash_mla_with_kvcache(q, kv, None, None, 512, sched, None, w.sm_scale, False, True, idx)
+        copy = out.clone()                # the next kernel in the stream; no host synchronisation in between
+        out.zero_()                       # and the one after it, so a late attention kernel would show in `out` too
+        torch.cuda.synchronize()
+        assert torch.equal(copy, ref)

@@ -48,6 +48,41 @@ def test_decode_full_batch_sampled_against_oracle(layout, b, s_q, lo, hi):
     check_decode(out2, lse2.contiguous(), out[half].cpu(), lse[half].cpu().contiguous(), strict=False)
 
 
+def test_mxfp8_decode_at_the_full_cache_size_sampled_against_oracle():
+    """The MXFP8 benchmark configuration as stated: b = 256, s_q = 1, every cache sequence 65536 tokens long, i.e. a
+    pool of 262144 pages (11 GB, row numbers up to 16.7 million).  The pool is written on the GPU by the cache writer
+    (fmla_kv_quantize) chunk by chunk from bf16 N(0,1) data; sampled requests are checked against the oracle, which
+    dequantises the very bytes the kernel reads."""
+    b, s_k, page, topk, h_q = 256, 65536, 64, 2048, 128
+    pages_per_seq = s_k // page
+    n_pages = b * pages_per_seq
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(43)
+    pool = torch.empty((n_pages, page, 1, 656), dtype=torch.uint8, device=DEV)
+    chunk = 8192
+    for lo in range(0, n_pages, chunk):
+        kv = torch.randn((chunk, page, 1, 576), generator=gen, device=DEV).to(torch.bfloat16)
+        flashmla_b200.quantize_k_cache(kv, wl.LAYOUT_MXFP8, out=pool[lo:lo + chunk])
+    del kv
+    block_table = torch.randperm(n_pages, generator=gen, device=DEV).to(torch.int32).view(b, pages_per_seq)
+    positions = wl.distinct_positions(torch.full((b,), s_k, dtype=torch.int32, device=DEV), topk, gen).view(b, 1, topk)
+    positions.masked_fill_(torch.rand(positions.shape, generator=gen, device=DEV) < 0.02, -1)
+    indices = flashmla_b200.abs_indices2indices_in_kvcache(positions, block_table, page)
+    assert int(indices.max()) > 2 ** 23, "the case is meant to reach high row numbers"
+    q = torch.randn((b, 1, h_q, 576), generator=gen, device=DEV).to(torch.bfloat16)
+    sm_scale = 576 ** -0.5
+    out, lse = flash_mla.flash_mla_with_kvcache(q, pool, None, None, 512, flash_mla.get_mla_metadata()[0], None, sm_scale,
+                                                False, True, indices, kvcache_layout=wl.LAYOUT_MXFP8)
+    assert flashmla_b200.kernel_status(DEV) == 0
+    assert bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(lse).all())
+    w = wl.DecodeWorkload(q=q, kv_rows=pool, kv_bf16=None, block_table=block_table,
+                          cache_seqlens=torch.full((b,), s_k, dtype=torch.int32), positions=positions, indices=indices,
+                          sm_scale=sm_scale, layout=wl.LAYOUT_MXFP8)
+    reqs = [0, 1, b // 2, b - 1]
+    ref_out, ref_lse = oracle_decode_requests(w, q, indices, reqs)
+    check_decode(out[reqs], lse[reqs].contiguous(), ref_out, ref_lse, strict=False)
+
+
 def test_prefill_full_size_sampled_against_oracle():
     """s_q=4096, s_kv=32768, h_q=128, topk=2048, causal offset 28672: a sample of query tokens against the
     oracle, and the whole output against a second run over a permuted top-k list (softmax is order-free)."""

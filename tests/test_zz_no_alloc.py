@@ -117,3 +117,26 @@ def test_static_scratch_rejects_what_does_not_fit_and_foreign_accumulators():
     assert b"must be null" in call.lib.fmla_last_error()
     torch.cuda.synchronize(DEV)
     assert int(call.status.item()) == 0
+
+
+def test_static_scratch_calls_leave_the_free_device_memory_unchanged():
+    """Callers of this entry point cannot allocate; neither may the entry point.  After the set-up call, further calls
+    made with buffers that already exist must leave the driver's free-memory figure where it was."""
+    w = wl.make_decode_workload(6, 1, 128, 1024, 1500, 4000, seed=33, invalid_frac=0.05)
+    call = DecodeCall(w, _lib.KERNEL_TC)
+    b, s_q, h_q = call.shape
+    a = call.args
+    out = torch.empty((b, s_q, h_q, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((b, s_q, h_q), dtype=torch.float32, device=DEV)
+    a.out, a.o_stride_b, a.o_stride_s, a.o_stride_h = out.data_ptr(), *out.stride()[:3]
+    a.lse, a.lse_stride_b, a.lse_stride_s = lse.data_ptr(), *lse.stride()[:2]
+    a.o_accum = a.lse_accum = None
+    _lib.check(call.lib.fmla_sparse_decode_static_scratch(C.byref(a), call.stream))     # set-up call
+    torch.cuda.synchronize(DEV)
+    free_before, _ = torch.cuda.mem_get_info(DEV)
+    for _ in range(3):
+        _lib.check(call.lib.fmla_sparse_decode_static_scratch(C.byref(a), call.stream))
+    torch.cuda.synchronize(DEV)
+    free_after, _ = torch.cuda.mem_get_info(DEV)
+    assert free_after == free_before
+    assert int(call.status.item()) == 0
