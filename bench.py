@@ -1,6 +1,7 @@
 """Benchmark of the sparse MLA hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|c2s|c4s|c5s] [--impl ours|reference]
+                    [--scaling weak|strong] [--no-also] [--no-cpu-baseline]
 
 Default workload "c2": FP8 sparse MLA decode at the DeepSeek-V3.2 shape (b=128, s_q=2, h_q=128,
 topk=2048, cache_seqlens uniform in [4096, 32768], 64-token pages in random order, ~2% invalid
@@ -8,9 +9,14 @@ indices), synthetic seeded data.  One step = one flash_mla_with_kvcache call (at
 combine kernel; the tile scheduler's output is cached after the first call, as in the reference's
 own timing, tests/kernelkit/bench.py:77-100).  Prints ONE JSON line on rank 0.
 
+On one GPU the default run also measures the other benchmark configurations for a few steps each
+(MXFP8 decode "c3", prefill forward "c4", prefill backward "c5") and reports them under "also".
+
 Multi-GPU (launched by torch.distributed.run): every rank owns its own sequences and KV pages
-(decode) or its own query tokens (prefill); there is no collective in the data path, so the run is
-weak-scaled: the per-GPU workload is fixed and the global batch is N times it.
+(decode) or its own query tokens (prefill); there is no collective in the data path.  The headline is
+weak-scaled (the per-GPU workload is fixed and the global batch is N times it); with more than one
+GPU the line also carries a "strong" record, the same global workload cut into N parts (b = 128 / N
+requests per GPU for c2), and for the backward the all-reduce of the per-GPU dKV partial sums.
 
 --impl reference times the CPU restatement of the reference's torch oracle (tests/ref.py) on the
 host cores, on a bounded sample of the same workload.
@@ -51,10 +57,13 @@ WORKLOADS = {
     "c5s": dict(kind="prefill_bwd", s_q=592, s_kv=32768, h_q=128, topk=2048, offset=28672,
                 name="sparse_prefill_bwd_sq592_skv32768_h128_topk2048"),
 }
-# DRAM bytes (read + write) of one attention-kernel launch, from the ncu captures summarised under profiles/
-NCU_TRAFFIC = {"c2": 420.2e6, "c2s": 52.52e6, "c4": 1.333e9, "c4s": 192.7e6}
+# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures summarised under profiles/
+# (captured on the reduced cases c2s / c4s / c5s and scaled by the units a full launch processes)
+NCU_TRAFFIC = {"c2": 411.5e6, "c2s": 51.43e6, "c4": 1.30e9, "c4s": 188.2e6}
 METRIC = {"decode": "fp8_sparse_mla_decode_tflops", "prefill_fwd": "sparse_prefill_fwd_tflops",
           "prefill_bwd": "sparse_prefill_bwd_tflops"}
+KERNEL_NAME = {"decode": "pair_attn_kernel<0,0>", "prefill_fwd": "pair_attn_kernel<1,0>",
+               "prefill_bwd": "bwd_scores_kernel + bwd_dq_dkv_kernel (tcgen05; the whole step)"}
 
 
 def peaks():
@@ -78,6 +87,7 @@ class ClockSampler:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+
             def reader():
                 for ln in self.proc.stdout:
                     self.lines.append((time.time(), ln))
@@ -118,11 +128,30 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_workload(cfg, device, seed):
+def bind_to_gpu_numa_node(local_rank: int) -> str:
+    """Binds this process to the CPUs next to its GPU (the PCI device's local_cpulist), so that pinned host buffers
+    allocated afterwards come from that NUMA node.  Changes nothing on the GPU; returns a note for the JSON line."""
+    try:
+        prop = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        cpus = set()
+        for part in open(f"/sys/bus/pci/devices/{bdf}/local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return f"bound to {len(cpus)} CPUs local to GPU {bdf}"
+    except (OSError, ValueError, AttributeError):
+        pass
+    return "not bound"
+
+
+def make_workload(cfg, device, seed, units=None):
     if cfg["kind"] == "decode":
-        return wl.make_decode_workload(cfg["b"], cfg["s_q"], cfg["h_q"], cfg["topk"], cfg["lo"], cfg["hi"],
+        return wl.make_decode_workload(units or cfg["b"], cfg["s_q"], cfg["h_q"], cfg["topk"], cfg["lo"], cfg["hi"],
                                        layout=cfg["layout"], seed=seed, device=device, invalid_frac=0.02, keep_bf16=False)
-    return wl.make_prefill_workload(cfg["s_q"], cfg["s_kv"], cfg["h_q"], cfg["topk"], seed=seed, device=device,
+    return wl.make_prefill_workload(units or cfg["s_q"], cfg["s_kv"], cfg["h_q"], cfg["topk"], seed=seed, device=device,
                                     causal_offset=cfg["offset"])
 
 
@@ -135,7 +164,7 @@ def cpu_step(cfg, w_cpu, sample):
     if cfg["kind"] == "decode":
         idx = w_cpu.indices[:sample]
         b, s_q, topk = idx.shape
-        rows = w_cpu.kv_rows.view(-1, 1, 1, 656)[idx.clamp_min(0).reshape(-1).long()].view(b * s_q * topk, 1, 1, 656)
+        rows = w_cpu.kv_rows.reshape(-1, 1, 1, 656)[idx.clamp_min(0).reshape(-1).long()].view(b * s_q * topk, 1, 1, 656)
         deq = quant.dequantize_rows(rows, w_cpu.layout)
         local = torch.arange(b * s_q * topk, dtype=torch.int32).view(b, s_q, topk).masked_fill(idx < 0, -1)
         attention.sparse_decode(w_cpu.q[:sample], deq, local, w_cpu.sm_scale)
@@ -156,8 +185,14 @@ def cpu_workload(cfg, sample, seed):
                                     causal_offset=cfg["offset"])
 
 
-def cpu_baseline(cfg, seed, budget_s=12.0):
-    cores = os.cpu_count() or 1
+def host_threads(world: int) -> int:
+    """The host cores this process may use: its share of the machine when several ranks run (torchrun sets
+    OMP_NUM_THREADS=1, which would otherwise leave the oracle on one core)."""
+    return max(1, len(os.sched_getaffinity(0)) // max(world, 1))
+
+
+def cpu_baseline(cfg, seed, world, budget_s=12.0):
+    cores = host_threads(world)
     torch.set_num_threads(cores)
     sample = 4 if cfg["kind"] == "decode" else 32
     w_cpu = cpu_workload(cfg, sample, seed)
@@ -175,10 +210,10 @@ def cpu_baseline(cfg, seed, budget_s=12.0):
             "sample": f"{reps} passes over the first {sample} {unit} of the workload ({dt:.1f} s), torch fp32 oracle, {cores} threads"}
 
 
-def run_reference(args, cfg, rank):
+def run_reference(args, cfg, rank, world):
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
+    cores = len(os.sched_getaffinity(0))     # rank 0 alone runs: it may use every core
     torch.set_num_threads(cores)
     sample = 16 if cfg["kind"] == "decode" else 64
     w_cpu = cpu_workload(cfg, sample, args.seed)
@@ -205,6 +240,206 @@ def run_reference(args, cfg, rank):
 # ------------------------------------------------------------------------------------------------
 # GPU leg
 # ------------------------------------------------------------------------------------------------
+class Bench:
+    """One workload on this rank's GPU: the device-timed step, the end-to-end step and their bookkeeping."""
+
+    def __init__(self, cfg, dev, seed, units=None):
+        import flash_mla
+        self.cfg, self.dev, self.kind = cfg, dev, cfg["kind"]
+        self.units = units or cfg.get("b", cfg.get("s_q"))
+        w = self.w = make_workload(cfg, dev, seed, units)
+        fm = flash_mla
+        if self.kind == "decode":
+            self.sched = fm.get_mla_metadata()[0]
+            self.flops, self.alg_bytes, self.launches = w.flops, w.algorithmic_bytes, 2
+            self.step = lambda q=w.q, idx=w.indices, mid=None: fm.flash_mla_with_kvcache(
+                q, w.kv_rows, None, None, 512, self.sched, None, w.sm_scale, False, True, idx, kvcache_layout=w.layout,
+                attn_done_event=mid)
+            self.inputs = [w.q, w.indices]
+            self.results = lambda r: [r[0], r[1].transpose(1, 2)]
+        elif self.kind == "prefill_fwd":
+            self.flops, self.alg_bytes, self.launches = w.fwd_flops, None, 1
+            self.step = lambda q=w.q, idx=w.indices: fm.flash_mla_sparse_fwd(q, w.kv, idx, w.sm_scale)
+            self.inputs = [w.q, w.indices]
+            self.results = lambda r: [r[0], r[2]]
+        else:
+            from flashmla_b200 import interface as itf
+            self.flops, self.alg_bytes = w.bwd_flops, None
+            # memset + passes of 592 tokens x (scores kernel, dq+dkv kernel) + fp32 -> bf16 cast
+            self.passes = -(-self.units // itf.BWD_CHUNK_TOKENS)
+            self.launches = 2 * self.passes + 1
+            out_f, _, lse_f = fm.flash_mla_sparse_fwd(w.q, w.kv, w.indices, w.sm_scale)
+            self.step = lambda q=w.q, idx=w.indices, dout=w.dout, ev=None: fm.flash_mla_sparse_bwd(
+                q, w.kv, out_f, dout, idx, lse_f, w.sm_scale, grad_events=ev)
+            self.inputs = [w.q, w.indices, w.dout]
+            self.results = lambda r: [r[0], r[1]]
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    # -- device-timed -----------------------------------------------------------------------------
+    def timed(self, steps, barrier, mid=False):
+        """Per-step CUDA-event timing on the launching stream with an L2 flush before every step.
+
+        A spin kernel is queued first so that the host runs ahead of the device: a step's events then bracket
+        device work only, not the host's launch latency (a decode step is shorter than its Python call).
+        Returns the per-step times and, with `mid`, the times of the part the inner events bracket."""
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        starts, ends = [ev() for _ in range(steps)], [ev() for _ in range(steps)]
+        inner = [(ev(), ev()) for _ in range(steps)] if mid else None
+        keep = []
+        barrier()
+        torch.cuda._sleep(int(2e6 * (10 + 1.0 * steps)))      # about (10 + steps) ms at 2 GHz
+        for i in range(steps):
+            self.flush.fill_(i & 0xff)
+            starts[i].record()
+            if not mid:
+                keep.append(self.step())
+            elif self.kind == "decode":
+                keep.append(self.step(mid=inner[i][1]))
+            else:
+                keep.append(self.step(ev=inner[i]))
+            ends[i].record()
+        barrier()
+        total = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+        if not mid:
+            return total
+        if self.kind == "decode":       # start of the step .. event between the attention and the combine kernel
+            return total, [s.elapsed_time(m[1]) for s, m in zip(starts, inner)]
+        return total, [m[0].elapsed_time(m[1]) for m in inner]      # the first pass's dQ / dKV launch
+
+    # -- end to end ---------------------------------------------------------------------------------
+    def prepare_e2e(self):
+        """Pinned host copies of the per-step inputs and results, two sets of device input buffers, three streams."""
+        self.host_in = [t.cpu().pin_memory() for t in self.inputs]
+        first = self.results(self.step())
+        torch.cuda.synchronize()
+        self.host_out = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in first] for _ in range(2)]
+        self.dev_in = [[torch.empty_like(t) for t in self.inputs] for _ in range(2)]
+        self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self.h2d = sum(h.numel() * h.element_size() for h in self.host_in)
+        self.d2h = sum(h.numel() * h.element_size() for h in self.host_out[0])
+
+    def e2e(self, steps, barrier):
+        """`steps` calls through the public API with every step's inputs copied from pinned host memory and every
+        step's results copied back.  The copies run on their own streams with two sets of buffers, so that step
+        i+1's host-to-device copy and step i-1's device-to-host copy travel (PCIe is full duplex) while step i
+        computes; all of it lies between the two events.  Returns the milliseconds per step."""
+        main = torch.cuda.current_stream(self.dev)
+        in_done = [torch.cuda.Event() for _ in range(2)]
+        free_in = [torch.cuda.Event() for _ in range(2)]      # the compute of the step that read this buffer set is over
+        out_done = [torch.cuda.Event() for _ in range(2)]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        keep = []
+        barrier()
+        start.record(main)
+        self.s_in.wait_event(start)
+        self.s_out.wait_event(start)
+        for i in range(steps):
+            k = i & 1
+            with torch.cuda.stream(self.s_in):
+                if i >= 2:
+                    self.s_in.wait_event(free_in[k])
+                for d, h in zip(self.dev_in[k], self.host_in):
+                    d.copy_(h, non_blocking=True)
+                in_done[k].record(self.s_in)
+            main.wait_event(in_done[k])
+            res = self.results(self.step(*self.dev_in[k]))
+            free_in[k].record(main)
+            computed = torch.cuda.Event()
+            computed.record(main)
+            keep.append(res)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(computed)
+                for h, t in zip(self.host_out[k], res):
+                    h.copy_(t, non_blocking=True)
+                out_done[k].record(self.s_out)
+        main.wait_stream(self.s_out)
+        end.record(main)
+        barrier()
+        return start.elapsed_time(end) / steps
+
+    # -- host cost of a call ------------------------------------------------------------------------
+    def host_us_per_call(self, n=200):
+        """Host time of one call (Python + C ABI + launches) with the device kept busy behind it, and of one replay
+        of the same call captured in a CUDA graph."""
+        if self.kind == "prefill_bwd":
+            return None
+        self.step(); torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            self.step()
+        eager = (time.perf_counter() - t0) / n * 1e6
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                captured = self.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            graph.replay()
+        replay = (time.perf_counter() - t0) / n * 1e6
+        torch.cuda.synchronize()
+        del captured
+        return {"eager": round(eager, 1), "graph_replay": round(replay, 1),
+                "note": "host time per call, device work queued behind it; the eager call encodes no tensor map after the first (they are cached)"}
+
+
+def measure(bench: Bench, clk: ClockSampler, steps, warmup, barrier, world, dev, all_reduce_max):
+    """Warm-up, device-timed steps (measured once more when the clocks were throttled or a step stalled) and the
+    attention kernel's own time.  Returns (ms per step, ms of the roofline kernel per launch, clocks)."""
+    for _ in range(warmup):
+        bench.step()
+    torch.cuda.synchronize()
+    attempts = []
+    for attempt in range(2):
+        t0 = time.time()
+        ms = ms_k = bench.timed(steps, barrier)
+        if bench.kind != "prefill_fwd":
+            # a second pass with timing events inside the step: decode - between the attention and the combine kernel
+            # (the event turns the combine kernel's dependent launch off, so `value` comes from the first pass);
+            # backward - around the first pass's dQ / dKV launch
+            _, ms_k = bench.timed(steps, barrier, mid=True)
+        t_end = time.time() + 6.0
+        while clk.count(t0) < 4 and time.time() < t_end:     # keep the load up until nvidia-smi has delivered samples
+            bench.step()
+            torch.cuda.synchronize()
+        cl = clk.summary(t0, time.time())
+        attempts.append((ms, ms_k, cl))
+        # a measurement taken under a thermal / hardware slowdown, with SM clocks far below their maximum, or with a
+        # step that stalled (another tenant of the host, a host hiccup) is taken once more
+        bad = [r for r in cl["reasons"] if r != "sw_power_cap"]
+        slow_clock = cl["sm_mhz"] is not None and cl["sm_mhz"] < 0.8 * cl["sm_max_mhz"]
+        stalled = max(ms) > 1.5 * statistics.median(ms)
+        if all_reduce_max(1 if (bad or slow_clock or stalled) else 0) == 0:   # the ranks decide together: timed() holds barriers
+            break
+    ms, ms_k, clocks = attempts[-1]
+    clocks["attempts"] = len(attempts)
+    return ms, ms_k, clocks
+
+
+def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
+    """The roofline object of a workload: the tensor pipe bounds all of them (SURVEY of the reference's own
+    flop model: tests/lib.py:345-402)."""
+    if bench.kind == "prefill_bwd":
+        # t_kernel = the first pass's dQ / dKV launch: its fp32 reductions into dKV are the traffic that matters there
+        units = min(bench.units, 592)
+        red_bytes = units * bench.cfg["topk"] * 576 * 4.0
+        return {"bound": "tensor", "achieved": bench.flops / t_step / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": bench.flops / t_step / 1e12 / pk["bf16_tflops"], "traffic": NCU_TRAFFIC.get(key), "basis": pk["basis"],
+                "kernel": KERNEL_NAME[bench.kind], "ms_per_launch": t_step * 1e3,
+                "dkv_reduction": {"bytes_per_pass": red_bytes, "ms_dq_dkv_launch": t_kernel * 1e3,
+                                  "achieved_gbs": red_bytes / t_kernel / 1e9,
+                                  "note": "fp32 red.global.add traffic of the first pass's dQ / dKV launch (592 query tokens x topk x 576 x 4 B) over its CUDA-event time"},
+                "note": "the whole step (all launches), 2*h_q*topk*(3*576+2*512) flops per query token"}
+    return {"bound": "tensor", "achieved": bench.flops / t_kernel / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": bench.flops / t_kernel / 1e12 / pk["bf16_tflops"], "traffic": NCU_TRAFFIC.get(key), "basis": pk["basis"],
+            "kernel": KERNEL_NAME[bench.kind], "ms_per_launch": t_kernel * 1e3,
+            "note": "the attention kernel alone (one launch per step), 2*h_q*topk*(576+512) flops per query token; "
+                    "traffic = DRAM bytes of one launch from the ncu capture under profiles/"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -212,8 +447,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="strong: the headline is the global workload cut into N parts instead of N copies of it")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the other configurations of the default run")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -221,187 +459,136 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, cfg, rank)
+        run_reference(args, cfg, rank, world)
         return
 
-    import flash_mla
     import torch.distributed as dist
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # The CPU baseline runs on rank 0 before the ranks meet, on rank 0's share of the cores: the other ranks then
+    # wait in the rendezvous (a host wait), not in a collective that would keep their GPUs spinning.
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(cfg, args.seed, world)
+    numa = bind_to_gpu_numa_node(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     args.warmup = max(args.warmup, 3)
-
-    w = make_workload(cfg, dev, args.seed + rank)
     kind = cfg["kind"]
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
-    ev_mid = torch.cuda.Event(enable_timing=True)
-
-    if kind == "decode":
-        sched = flash_mla.get_mla_metadata()[0]
-        flops, alg_bytes = w.flops, w.algorithmic_bytes
-        launches_per_step = 2
-
-        def step(q=w.q, idx=w.indices, mid=None):
-            return flash_mla.flash_mla_with_kvcache(q, w.kv_rows, None, None, 512, sched, None, w.sm_scale, False, True,
-                                                    idx, kvcache_layout=w.layout, attn_done_event=mid)
-        host_in = [w.q.cpu().pin_memory(), w.indices.cpu().pin_memory()]
-        host_out = [torch.empty((cfg["b"], cfg["s_q"], cfg["h_q"], 512), dtype=torch.bfloat16).pin_memory(),
-                    torch.empty((cfg["b"], cfg["s_q"], cfg["h_q"]), dtype=torch.float32).pin_memory()]
-
-        def e2e_step():
-            q = host_in[0].to(dev, non_blocking=True)
-            idx = host_in[1].to(dev, non_blocking=True)
-            out, lse = step(q, idx)
-            host_out[0].copy_(out, non_blocking=True)
-            host_out[1].copy_(lse.transpose(1, 2), non_blocking=True)
-            return host_out
-    elif kind == "prefill_fwd":
-        flops, alg_bytes = w.fwd_flops, None
-        launches_per_step = 1
-
-        def step(q=w.q, idx=w.indices):
-            return flash_mla.flash_mla_sparse_fwd(q, w.kv, idx, w.sm_scale)
-        host_in = [w.q.cpu().pin_memory(), w.indices.cpu().pin_memory()]
-        host_out = [torch.empty((cfg["s_q"], cfg["h_q"], 512), dtype=torch.bfloat16).pin_memory(),
-                    torch.empty((cfg["s_q"], cfg["h_q"]), dtype=torch.float32).pin_memory()]
-
-        def e2e_step():
-            q = host_in[0].to(dev, non_blocking=True)
-            idx = host_in[1].to(dev, non_blocking=True)
-            out, mx, lse = step(q, idx)
-            host_out[0].copy_(out, non_blocking=True)
-            host_out[1].copy_(lse, non_blocking=True)
-            return host_out
-    else:
-        flops, alg_bytes = w.bwd_flops, None
-        # memset + 7 passes of 592 tokens x (scores kernel, dq+dkv kernel) + fp32 -> bf16 cast
-        from flashmla_b200 import interface as _itf
-        launches_per_step = 2 * -(-cfg["s_q"] // _itf.BWD_CHUNK_TOKENS) + 1
-        out_f, _, lse_f = flash_mla.flash_mla_sparse_fwd(w.q, w.kv, w.indices, w.sm_scale)
-
-        def step(q=w.q, idx=w.indices, dout=w.dout):
-            return flash_mla.flash_mla_sparse_bwd(q, w.kv, out_f, dout, idx, lse_f, w.sm_scale)
-        host_in = [w.q.cpu().pin_memory(), w.indices.cpu().pin_memory(), w.dout.cpu().pin_memory()]
-
-        host_out = [torch.empty((cfg["s_q"], cfg["h_q"], 576), dtype=torch.bfloat16).pin_memory(),
-                    torch.empty((cfg["s_kv"], 1, 576), dtype=torch.bfloat16).pin_memory()]
-
-        def e2e_step():
-            t = [h.to(dev, non_blocking=True) for h in host_in]
-            dq, dkv = step(*t)
-            host_out[0].copy_(dq, non_blocking=True)
-            host_out[1].copy_(dkv, non_blocking=True)
-            return host_out
+    full_units = cfg.get("b", cfg.get("s_q"))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, with_mid=False):
-        """Per-step CUDA-event timing on the launching stream with an L2 flush before every step.
+    def all_reduce_max(v):
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-        A spin kernel is queued first so that the host runs ahead of the device: a step's events then bracket
-        device work only, not the host's launch latency (a decode step is shorter than its Python call).
-        Returns the per-step times and, with `with_mid`, the times up to the event between the two kernels."""
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        mids = [torch.cuda.Event(enable_timing=True) for _ in range(steps)] if with_mid else None
-        keep = []
-        barrier()
-        torch.cuda._sleep(int(2e6 * (10 + 1.0 * steps)))      # about (10 + steps) ms at 2 GHz
-        for i in range(steps):
-            flush.fill_(i & 0xff)
-            starts[i].record()
-            keep.append(fn(mid=mids[i]) if with_mid else fn())
-            ends[i].record()
-        barrier()
-        total = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-        return (total, [s.elapsed_time(m) for s, m in zip(starts, mids)]) if with_mid else total
-
+    strong_units = max(1, full_units // world)
+    head_units = strong_units if args.scaling == "strong" else full_units
+    line = None
     # nvidia-smi is started before the warm-up: its start-up queries stall kernel launches for milliseconds
     with ClockSampler(local_rank) as clk:
+        bench = Bench(cfg, dev, args.seed + rank, head_units)
+        bench.prepare_e2e()
         for _ in range(args.warmup):
-            step()
-            e2e_step()
-        torch.cuda.synchronize()
+            bench.e2e(2, barrier)
         t_wait = time.time() + 5.0
         while not clk.lines and time.time() < t_wait:      # first sample delivered = start-up over
-            step()
+            bench.step()
             torch.cuda.synchronize()
-        attempts = []
-        for attempt in range(2):
-            t0 = time.time()
-            ms = ms_attn = timed(step, args.steps)
-            if kind == "decode":
-                # a second pass with a timing event between the attention and the combine kernel gives the attention
-                # kernel's own time for the roofline (the event turns the combine kernel's dependent launch off, so
-                # the figure reported as `value` comes from the first, uninstrumented pass)
-                _, ms_attn = timed(step, args.steps, with_mid=True)
-            # the same step keeps running until nvidia-smi has delivered a few samples under load
-            t_end = time.time() + 6.0
-            while clk.count(t0) < 4 and time.time() < t_end:
-                step()
-                torch.cuda.synchronize()
-            t1 = time.time()
-            cl = clk.summary(t0, t1)
-            attempts.append((ms, ms_attn, cl))
-            # a measurement taken under a thermal / hardware slowdown, with SM clocks far below their maximum, or
-            # with a step that stalled (another tenant of the host, a host hiccup) is taken once more
-            bad = [r for r in cl["reasons"] if r != "sw_power_cap"]
-            slow_clock = cl["sm_mhz"] is not None and cl["sm_mhz"] < 0.8 * cl["sm_max_mhz"]
-            stalled = max(ms) > 1.5 * statistics.median(ms)
-            retry = torch.tensor([1 if (bad or slow_clock or stalled) else 0], dtype=torch.int32, device=dev)
-            if world > 1:                       # the ranks take the decision together: timed() holds barriers
-                dist.all_reduce(retry, op=dist.ReduceOp.MAX)
-            if int(retry.item()) == 0:
-                break
-        ms, ms_attn, clocks = attempts[-1]
-        clocks["attempts"] = len(attempts)
-    if os.environ.get("FMLA_BENCH_VERBOSE"):
-        print("per-step ms:", [round(x, 3) for x in ms], file=sys.stderr)
-    ms_e2e = timed(e2e_step, args.steps)
-
-    total_ms = torch.tensor([sum(ms), sum(ms_e2e)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
-    t_kernel, t_e2e = (total_ms / args.steps / 1e3).tolist()
-
-    if rank == 0:
+        ms, ms_k, clocks = measure(bench, clk, args.steps, args.warmup, barrier, world, dev, all_reduce_max)
+        if os.environ.get("FMLA_BENCH_VERBOSE"):
+            print("per-step ms:", [round(x, 3) for x in ms], file=sys.stderr)
+        t_step = all_reduce_max(sum(ms)) / args.steps / 1e3
+        t_e2e = all_reduce_max(bench.e2e(args.steps, barrier)) / 1e3
+        host_us = bench.host_us_per_call() if rank == 0 else None
         pk = peaks()
-        t_attn = sum(ms_attn) / args.steps / 1e3
-        value = world * flops / t_kernel / 1e12
-        h2d = sum(h.numel() * h.element_size() for h in host_in)
-        outs = e2e_step()
-        torch.cuda.synchronize()
-        d2h = sum(o.numel() * o.element_size() for o in outs)
-        line = {
-            "metric": METRIC[kind], "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": t_kernel * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": (value / world / 350.0) if args.workload == "c2" else (value / world / 1450.0 if args.workload == "c4" else None),
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg["name"], "per_gpu_units": cfg.get("b", cfg.get("s_q")),
-                       "global_units": cfg.get("b", cfg.get("s_q")) * world,
-                       "timing": "CUDA events per step on the launching stream, 256 MB L2 flush before every step, max over ranks",
-                       "baseline_note": "vs_baseline divides the per-GPU value by the reference README's B200 figure (350 TFLOPS decode / 1450 prefill), whose exact shape is not published"},
-            "gpu_launches": launches_per_step * args.steps,
-            "e2e": {"value": world * flops / t_e2e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": t_e2e * 1e3,
-                    "note": "q and indices copied from pinned host memory and out, lse copied back every step; the paged KV cache is resident serving state"},
-            "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": flops / t_attn / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": flops / t_attn / 1e12 / pk["bf16_tflops"], "traffic": NCU_TRAFFIC.get(args.workload),
-                         "basis": pk["basis"], "kernel": "pair_attn_kernel" if kind != "prefill_bwd" else "bwd_scores_kernel + bwd_dq_dkv_kernel (tcgen05; the whole step, 2*h_q*topk*(3*576+2*512) flops per query token)", "ms_per_launch": t_attn * 1e3,
-                         "note": "rank 0's attention kernel alone (one launch per step), 2*h_q*topk*(576+512) flops per "
-                                 "query token; traffic = DRAM bytes of one launch from the ncu capture under profiles/"},
-        }
-        if alg_bytes is not None:
-            line["hbm"] = {"algorithmic_bytes": alg_bytes, "achieved_gbs": alg_bytes / t_kernel / 1e9,
-                           "frac_of_measured_copy": alg_bytes / t_kernel / 1e9 / pk["hbm_gbs"]}
-        if not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(cfg, args.seed)
+        if rank == 0:
+            t_kernel = sum(ms_k) / args.steps / 1e3
+            value = world * bench.flops / t_step / 1e12
+            per_gpu = value / world
+            line = {
+                "metric": METRIC[kind], "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": args.scaling,
+                "vs_baseline": (per_gpu / 350.0) if args.workload == "c2" else (per_gpu / 1450.0 if args.workload == "c4" else None),
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": cfg["name"], "per_gpu_units": head_units, "global_units": head_units * world,
+                           "timing": "CUDA events per step on the launching stream, 256 MB L2 flush before every step, max over ranks",
+                           "baseline_note": "vs_baseline divides the per-GPU value by the reference README's B200 figure (350 TFLOPS decode / 1450 prefill), whose exact shape is not published"},
+                "gpu_launches": bench.launches * args.steps,
+                "e2e": {"value": world * bench.flops / t_e2e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": bench.h2d,
+                        "d2h_bytes_per_step": bench.d2h, "ms_per_step": t_e2e * 1e3, "host_binding": numa,
+                        "note": "every step's q and indices (and dout) come from pinned host memory and its results go back; copy-in, "
+                                "compute and copy-out run on three streams with two buffer sets, so the copies of neighbouring "
+                                "steps overlap the compute; the paged KV cache is resident serving state; the inputs exceed L2"},
+                "clocks": clocks,
+                "roofline": roofline_record(bench, args.workload, t_step, t_kernel, pk),
+            }
+            if host_us:
+                line["host_us_per_call"] = host_us
+            if bench.alg_bytes is not None:
+                line["hbm"] = {"algorithmic_bytes": bench.alg_bytes, "achieved_gbs": bench.alg_bytes / t_step / 1e9,
+                               "frac_of_measured_copy": bench.alg_bytes / t_step / 1e9 / pk["hbm_gbs"]}
+            if cpu is not None:
+                line["cpu_baseline"] = cpu
+
+        # ---- backward on several GPUs: the per-GPU dKV partial sums are added with one NCCL all-reduce after the kernels
+        if kind == "prefill_bwd" and world > 1:
+            dkv = torch.zeros((cfg["s_kv"], 576), dtype=torch.float32, device=dev)
+            for _ in range(3):
+                dist.all_reduce(dkv)
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            s.record()
+            for _ in range(10):
+                dist.all_reduce(dkv)
+            e.record()
+            torch.cuda.synchronize()
+            t_red = all_reduce_max(s.elapsed_time(e) / 10)
+            if rank == 0:
+                line["dkv_all_reduce"] = {"bytes": dkv.numel() * 4, "ms": t_red, "ms_kernels_plus_reduce": t_step * 1e3 + t_red,
+                                          "note": "NCCL all-reduce of the fp32 [s_kv, 576] partial sums, issued after the kernels; "
+                                                  "`value` is the kernels alone"}
+
+        # ---- the same global workload cut into N parts (BASELINE's partition: 128 / N requests per GPU)
+        if world > 1 and args.scaling == "weak" and strong_units < full_units:
+            del bench
+            torch.cuda.empty_cache()
+            sb = Bench(cfg, dev, args.seed + 100 + rank, strong_units)
+            s_ms, s_k, s_clocks = measure(sb, clk, args.steps, args.warmup, barrier, world, dev, all_reduce_max)
+            ts = all_reduce_max(sum(s_ms)) / args.steps / 1e3
+            if rank == 0:
+                line["strong"] = {"value": world * sb.flops / ts / 1e12, "unit": "TFLOP/s", "ms_per_step": ts * 1e3,
+                                  "per_gpu_units": strong_units, "global_units": strong_units * world, "clocks": s_clocks,
+                                  "roofline_frac_per_gpu": roofline_record(sb, None, ts, sum(s_k) / args.steps / 1e3, pk)["frac"],
+                                  "note": "the global workload of one GPU's run cut into N parts; compare with the N = 1 value"}
+            del sb
+        elif world == 1 and args.workload == "c2" and not args.no_also:
+            # ---- the other benchmark configurations, a few steps each
+            del bench
+            also = {}
+            for key, steps in (("c3", 6), ("c4", 3), ("c5", 2)):
+                torch.cuda.empty_cache()
+                c = WORKLOADS[key]
+                ob = Bench(c, dev, args.seed + 7)
+                o_ms, o_k, o_clocks = measure(ob, clk, steps, 3, barrier, world, dev, all_reduce_max)
+                t = sum(o_ms) / steps / 1e3
+                rec = {"workload": c["name"], "metric": METRIC[c["kind"]], "value": ob.flops / t / 1e12, "unit": "TFLOP/s",
+                       "steps": steps, "ms_per_step": t * 1e3, "clocks": o_clocks,
+                       "roofline": roofline_record(ob, key, t, sum(o_k) / steps / 1e3, pk)}
+                if ob.alg_bytes is not None:
+                    rec["hbm_achieved_gbs"] = ob.alg_bytes / t / 1e9
+                also[key] = rec
+                del ob
+            line["also"] = also
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

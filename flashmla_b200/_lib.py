@@ -76,6 +76,7 @@ class PrefillBwdArgs(C.Structure):
         ("attn_sink", C.c_void_p), ("topk_length", C.c_void_p),
         ("dq", C.c_void_p), ("dkv_accum", C.c_void_p), ("dkv", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64), ("status", C.c_void_p),
+        ("grad_begin_event", C.c_void_p), ("grad_end_event", C.c_void_p),
     ]
 
 

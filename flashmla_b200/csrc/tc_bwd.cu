@@ -673,8 +673,11 @@ int launch_tc_prefill_bwd(const FmlaPrefillBwdArgs& a, cudaStream_t stream) {
     p.unit0 = (int)u0;
     bwd_scores_kernel<<<n, sc::THREADS, sc::SMEM, stream>>>(p);
     FMLA_CUDA(cudaGetLastError());
+    const bool timed = u0 == 0 && a.grad_begin_event != nullptr && a.grad_end_event != nullptr;
+    if (timed) FMLA_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.grad_begin_event), stream));
     bwd_dq_dkv_kernel<<<dim3(GRAD_ROLES, n), GRAD_THREADS, GRAD_SMEM, stream>>>(p);
     FMLA_CUDA(cudaGetLastError());
+    if (timed) FMLA_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.grad_end_event), stream));
   }
   if (a.dkv != nullptr) {
     const int64_t n = (int64_t)a.s_kv * D_QK;

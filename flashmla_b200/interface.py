@@ -351,8 +351,12 @@ def flash_mla_sparse_bwd(
     attn_sink: Optional[torch.Tensor] = None,
     topk_length: Optional[torch.Tensor] = None,
     return_fp32_dkv: bool = False,
+    *,
+    grad_events: Optional[Tuple["torch.cuda.Event", "torch.cuda.Event"]] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Backward of ``flash_mla_sparse_fwd`` (no counterpart in the reference).
+
+    grad_events: an optional pair of timing events recorded around the first pass's dQ / dKV launch.
 
     out and lse are the forward's results, dout (s_q, h_q, 512) bf16.  Returns dq (s_q, h_q, 576)
     bf16 and dkv (s_kv, 1, 576): gradients of all queries that index a token are added in fp32 and
@@ -386,6 +390,11 @@ def flash_mla_sparse_bwd(
     ws_bytes = lib.fmla_sparse_prefill_bwd_workspace(min(s_q, BWD_CHUNK_TOKENS), h_q, topk, a.kernel)
     workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev) if ws_bytes > 0 else None
     a.workspace, a.workspace_bytes, a.status = _ptr(workspace), ws_bytes, _status(dev).data_ptr()
+    if grad_events is not None:
+        for ev in grad_events:
+            if not ev.cuda_event:          # torch creates the CUDA event lazily, on the first record()
+                ev.record(torch.cuda.current_stream(dev))
+        a.grad_begin_event, a.grad_end_event = grad_events[0].cuda_event, grad_events[1].cuda_event
     _lib.check(lib.fmla_sparse_prefill_bwd(C.byref(a), _stream(dev)))
     return dq, (dkv_acc if return_fp32_dkv else dkv).view(s_kv, 1, D_QK)
 

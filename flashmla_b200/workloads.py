@@ -118,12 +118,26 @@ def make_decode_workload(
     block_table = torch.randperm(n_pages, generator=gen, device=device).to(torch.int32).view(b, pages_per_seq)
 
     q = (torch.randn((b, s_q, h_q, D_QK), generator=gen, device=device) * q_std)
-    kv = (torch.randn((n_pages, page, 1, D_QK), generator=gen, device=device) * kv_std)
     if clamp is not None:
         q.clamp_(-clamp, clamp)
-        kv.clamp_(-clamp, clamp)
     q = q.to(torch.bfloat16)
-    kv = kv.to(torch.bfloat16)
+    # A large pool whose bf16 source nobody needs is generated and quantised page chunk by page chunk, so that the
+    # fp32 temporaries stay small (the 11 GB pool of the MXFP8 configuration would otherwise need ~100 GB of them).
+    chunked = not keep_bf16 and not poison_unused and n_pages * page * D_QK > (1 << 28)
+    kv = None
+    if chunked:
+        kv_rows = torch.empty((n_pages, page + row_pad, 1, ROW_BYTES), dtype=torch.uint8, device=device)[:, :page]
+        step = max(1, (1 << 26) // (page * D_QK))
+        for lo in range(0, n_pages, step):
+            part = torch.randn((min(step, n_pages - lo), page, 1, D_QK), generator=gen, device=device) * kv_std
+            if clamp is not None:
+                part.clamp_(-clamp, clamp)
+            kv_rows[lo:lo + part.shape[0]] = quantize_kv_rows(part.to(torch.bfloat16), layout)
+    else:
+        kv = (torch.randn((n_pages, page, 1, D_QK), generator=gen, device=device) * kv_std)
+        if clamp is not None:
+            kv.clamp_(-clamp, clamp)
+        kv = kv.to(torch.bfloat16)
 
     positions = distinct_positions(seqlens.repeat_interleave(s_q), topk, gen).view(b, s_q, topk)
     if invalid_tail:
@@ -151,7 +165,8 @@ def make_decode_workload(
         keep[used[used >= 0].to(torch.int64)] = True
         kv.view(-1, D_QK)[~keep] = float("nan")
 
-    kv_rows = quantize_kv_rows(kv, layout, row_pad=row_pad)
+    if not chunked:
+        kv_rows = quantize_kv_rows(kv, layout, row_pad=row_pad)
     return DecodeWorkload(
         q=q, kv_rows=kv_rows, kv_bf16=kv if keep_bf16 else None, block_table=block_table,
         cache_seqlens=seqlens, positions=positions, indices=indices,

@@ -216,6 +216,8 @@ typedef struct {
                                     processed in as many chunks as the size makes necessary */
   int64_t workspace_bytes;
   int32_t* status;               /* optional, as in FmlaDecodeArgs */
+  void* grad_begin_event;        /* optional cudaEvent_t pair recorded on the stream around the first pass's dQ / dKV */
+  void* grad_end_event;          /* launch (tensor-core kernels), so that a caller can time that launch; null = not recorded */
 } FmlaPrefillBwdArgs;
 int fmla_sparse_prefill_bwd(const FmlaPrefillBwdArgs* args, void* cuda_stream);
 /* Workspace bytes with which `s_q` query tokens go through the tensor-core backward in one chunk (0 when the
