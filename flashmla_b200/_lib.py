@@ -14,7 +14,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FLASHMLA_B200_LIB") or os.path.join(_PKG, "lib", "libflashmla_b200.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_ARCH, ERR_TIMEOUT = range(7)
-LAYOUT_V32, LAYOUT_MXFP8 = 0, 1
+LAYOUT_V32, LAYOUT_MXFP8, LAYOUT_MODEL1 = 0, 1, 2
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
 SCHED_META_INTS = 8
 STATIC_SCRATCH_ROWS = 16384
@@ -62,6 +62,7 @@ class PrefillArgs(C.Structure):
         ("indices", C.c_void_p), ("idx_stride_s", C.c_int64),
         ("attn_sink", C.c_void_p), ("topk_length", C.c_void_p),
         ("out", C.c_void_p), ("max_logits", C.c_void_p), ("lse", C.c_void_p), ("status", C.c_void_p),
+        ("d_qk", C.c_int),
     ]
 
 

@@ -110,8 +110,9 @@ int fmla_sparse_decode(const FmlaDecodeArgs* a, void* cuda_stream) {
   FMLA_REQUIRE(a != nullptr, FMLA_ERR_INVALID_ARG, "sparse_decode: null argument struct");
   FMLA_REQUIRE(a->b > 0 && a->s_q > 0 && a->h_q > 0 && a->topk > 0, FMLA_ERR_INVALID_ARG,
                "sparse_decode: b=%d s_q=%d h_q=%d topk=%d must be positive", a->b, a->s_q, a->h_q, a->topk);
-  FMLA_REQUIRE(a->layout == FMLA_LAYOUT_V32 || a->layout == FMLA_LAYOUT_MXFP8, FMLA_ERR_UNSUPPORTED,
+  FMLA_REQUIRE(a->layout == FMLA_LAYOUT_V32 || a->layout == FMLA_LAYOUT_MXFP8 || a->layout == FMLA_LAYOUT_MODEL1, FMLA_ERR_UNSUPPORTED,
                "sparse_decode: unknown KV layout %d", a->layout);
+  const int64_t row_bytes = a->layout == FMLA_LAYOUT_MODEL1 ? FMLA_MODEL1_ROW_BYTES : FMLA_ROW_BYTES;
   FMLA_REQUIRE(a->q && a->kv && a->indices && a->out && a->lse, FMLA_ERR_INVALID_ARG,
                "sparse_decode: q, kv, indices, out and lse must be non-null");
   FMLA_REQUIRE(a->sched_meta && a->num_splits && a->o_accum && a->lse_accum && a->num_sm_parts > 0, FMLA_ERR_INVALID_ARG,
@@ -121,8 +122,10 @@ int fmla_sparse_decode(const FmlaDecodeArgs* a, void* cuda_stream) {
                (long long)a->page_block_size);
   FMLA_REQUIRE(a->num_blocks * a->page_block_size <= 0x7fffffffLL, FMLA_ERR_UNSUPPORTED,
                "sparse_decode: the cache holds more rows than an int32 index can address");
-  FMLA_REQUIRE(a->kv_stride_block >= a->page_block_size * FMLA_ROW_BYTES, FMLA_ERR_INVALID_ARG,
-               "sparse_decode: kv block stride %lld is smaller than page_block_size*656", (long long)a->kv_stride_block);
+  FMLA_REQUIRE(a->kv_stride_block >= a->page_block_size * row_bytes, FMLA_ERR_INVALID_ARG,
+               "sparse_decode: kv block stride %lld is smaller than page_block_size*%lld", (long long)a->kv_stride_block, (long long)row_bytes);
+  // MODEL1 blocks hold their data rows at a pitch of 576 bytes, so 16-byte row alignment needs a block stride that is a
+  // multiple of 16 as well (the reference pads its blocks to a multiple of 576, tests/quant.py:57-58)
   FMLA_REQUIRE(aligned16(a->kv) && a->kv_stride_block % 16 == 0, FMLA_ERR_ALIGNMENT,
                "sparse_decode: kv base and block stride must be multiples of 16 bytes");
   FMLA_REQUIRE(aligned16(a->q) && a->q_stride_b % 8 == 0 && a->q_stride_s % 8 == 0 && a->q_stride_h % 8 == 0,
@@ -139,8 +142,8 @@ int fmla_sparse_decode(const FmlaDecodeArgs* a, void* cuda_stream) {
                      a->extra_num_blocks * a->extra_page_block_size <= 0x7fffffffLL, FMLA_ERR_INVALID_ARG,
                  "sparse_decode: extra cache of %lld blocks x %lld rows is empty or holds more rows than an int32 index can address",
                  (long long)a->extra_num_blocks, (long long)a->extra_page_block_size);
-    FMLA_REQUIRE(a->extra_kv_stride_block >= a->extra_page_block_size * FMLA_ROW_BYTES, FMLA_ERR_INVALID_ARG,
-                 "sparse_decode: extra kv block stride %lld is smaller than page_block_size*656", (long long)a->extra_kv_stride_block);
+    FMLA_REQUIRE(a->extra_kv_stride_block >= a->extra_page_block_size * row_bytes, FMLA_ERR_INVALID_ARG,
+                 "sparse_decode: extra kv block stride %lld is smaller than page_block_size*%lld", (long long)a->extra_kv_stride_block, (long long)row_bytes);
     FMLA_REQUIRE(aligned16(a->extra_kv) && a->extra_kv_stride_block % 16 == 0, FMLA_ERR_ALIGNMENT,
                  "sparse_decode: extra kv base and block stride must be multiples of 16 bytes");
   } else {
@@ -170,6 +173,8 @@ int fmla_sparse_prefill_fwd(const FmlaPrefillArgs* a, void* cuda_stream) {
                "sparse_prefill_fwd: s_q=%d s_kv=%d h_q=%d topk=%d must be positive", a->s_q, a->s_kv, a->h_q, a->topk);
   FMLA_REQUIRE(a->q && a->kv && a->indices && a->out && a->max_logits && a->lse, FMLA_ERR_INVALID_ARG,
                "sparse_prefill_fwd: q, kv, indices, out, max_logits and lse must be non-null");
+  FMLA_REQUIRE(a->d_qk == 0 || a->d_qk == FMLA_D_QK || a->d_qk == FMLA_MODEL1_D_QK, FMLA_ERR_UNSUPPORTED,
+               "sparse_prefill_fwd: d_qk must be 576 or 512 (got %d)", a->d_qk);
   FMLA_REQUIRE(aligned16(a->q) && a->q_stride_s % 8 == 0 && a->q_stride_h % 8 == 0, FMLA_ERR_ALIGNMENT,
                "sparse_prefill_fwd: q base and strides must be multiples of 16 bytes");
   FMLA_REQUIRE(aligned16(a->kv) && a->kv_stride_s % 8 == 0, FMLA_ERR_ALIGNMENT,

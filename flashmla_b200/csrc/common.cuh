@@ -55,6 +55,8 @@ constexpr int D_ROPE = 64;
 constexpr int ROW_BYTES = FMLA_ROW_BYTES;
 constexpr int SCALE_OFF = 512;
 constexpr int ROPE_OFF = 528;
+// MODEL1 cache blocks: [page x 576 data bytes (448 e4m3 | 64 bf16)] [page x 8 scale bytes (7 e8m0 | pad)]
+constexpr int M1_D_QK = FMLA_MODEL1_D_QK, M1_D_NOPE = 448, M1_DATA_BYTES = FMLA_MODEL1_DATA_BYTES, M1_ROW_BYTES = FMLA_MODEL1_ROW_BYTES;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 

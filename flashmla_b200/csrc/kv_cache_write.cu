@@ -74,6 +74,47 @@ kv_quantize_kernel(const __nv_bfloat16* __restrict__ src, int64_t src_stride, ui
   if (lane < 8) *reinterpret_cast<uint4*>(out + 528 + 16 * lane) = ldg_nc_16(in + 512 + 8 * lane);
 }
 
+// MODEL1 (tests/quant.py:55-75): bf16 rows [512] -> per cache block [page x (448 e4m3 | 64 bf16)] [page x (7 e8m0 | pad)].
+// One warp per row; lane l holds the 16-byte chunks l and l + 32 of the 64 (chunks 0..55 NoPE, 56..63 RoPE); a scale
+// covers 64 values = 8 consecutive lanes.
+__global__ void __launch_bounds__(32 * QUANT_WARPS)
+kv_quantize_model1_kernel(const __nv_bfloat16* __restrict__ src, int64_t src_stride, uint8_t* __restrict__ dst, int64_t page,
+                          int64_t dst_block_stride, int64_t n_rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * QUANT_WARPS + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const __nv_bfloat16* in = src + row * src_stride;
+  uint8_t* block = dst + (row / page) * dst_block_stride;
+  uint8_t* out = block + (row % page) * M1_DATA_BYTES;
+  uint8_t* scales = block + page * M1_DATA_BYTES + (row % page) * 8;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int chunk = lane + 32 * k;
+    const uint4 raw = ldg_nc_16(in + 8 * chunk);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(bf16_bits_to_float(w[i] & 0xffffu)), fabsf(bf16_bits_to_float(w[i] >> 16))));
+    for (int d = 1; d < 8; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    if (chunk >= 56) {                                                   // RoPE: copied verbatim behind the 448 bytes
+      *reinterpret_cast<uint4*>(out + M1_D_NOPE + 16 * (chunk - 56)) = raw;
+      continue;
+    }
+    const uint32_t sbits = pow2_scale_bits(amax);
+    const float inv = __uint_as_float(0x7f000000u - sbits);              // 1 / 2^e = 2^-e, exact
+    uint32_t q[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t lo = __nv_cvt_float_to_fp8(bf16_bits_to_float(w[i] & 0xffffu) * inv, __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float_to_fp8(bf16_bits_to_float(w[i] >> 16) * inv, __NV_SATFINITE, __NV_E4M3);
+      q[i >> 1] |= (lo | (hi << 8)) << (16 * (i & 1));
+    }
+    *reinterpret_cast<uint2*>(out + 8 * chunk) = make_uint2(q[0], q[1]);
+    if ((chunk & 7) == 0) scales[chunk >> 3] = (uint8_t)(sbits >> 23);   // e8m0 = the biased exponent
+  }
+  if (lane == 0) scales[7] = 0;
+}
+
 __global__ void cache_index_kernel(const int* __restrict__ pos, const int* __restrict__ block_table, int* __restrict__ out,
                                    int64_t per_request, int64_t total, int page, int max_pages) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -97,21 +138,30 @@ extern "C" int fmla_kv_quantize(const FmlaKvQuantArgs* a, void* cuda_stream) {
   FMLA_REQUIRE(a != nullptr, FMLA_ERR_INVALID_ARG, "kv_quantize: null argument struct");
   FMLA_REQUIRE(a->n_rows > 0 && a->page_block_size > 0, FMLA_ERR_INVALID_ARG,
                "kv_quantize: n_rows=%lld page_block_size=%lld must be positive", (long long)a->n_rows, (long long)a->page_block_size);
-  FMLA_REQUIRE(a->layout == FMLA_LAYOUT_V32 || a->layout == FMLA_LAYOUT_MXFP8, FMLA_ERR_UNSUPPORTED,
+  FMLA_REQUIRE(a->layout == FMLA_LAYOUT_V32 || a->layout == FMLA_LAYOUT_MXFP8 || a->layout == FMLA_LAYOUT_MODEL1, FMLA_ERR_UNSUPPORTED,
                "kv_quantize: unknown KV layout %d", a->layout);
+  const bool m1 = a->layout == FMLA_LAYOUT_MODEL1;
+  const int d_qk = m1 ? M1_D_QK : D_QK;
+  const int64_t row_bytes = m1 ? M1_ROW_BYTES : ROW_BYTES;
   FMLA_REQUIRE(a->kv && a->rows, FMLA_ERR_INVALID_ARG, "kv_quantize: kv and rows must be non-null");
-  FMLA_REQUIRE((reinterpret_cast<uintptr_t>(a->kv) & 15u) == 0 && a->kv_stride_row % 8 == 0 && a->kv_stride_row >= D_QK, FMLA_ERR_ALIGNMENT,
-               "kv_quantize: kv must be 16-byte aligned with a row stride that is a multiple of 8 elements and at least 576");
+  FMLA_REQUIRE((reinterpret_cast<uintptr_t>(a->kv) & 15u) == 0 && a->kv_stride_row % 8 == 0 && a->kv_stride_row >= d_qk, FMLA_ERR_ALIGNMENT,
+               "kv_quantize: kv must be 16-byte aligned with a row stride that is a multiple of 8 elements and at least %d", d_qk);
   FMLA_REQUIRE((reinterpret_cast<uintptr_t>(a->rows) & 15u) == 0 && a->rows_stride_block % 16 == 0 &&
-                   a->rows_stride_block >= a->page_block_size * ROW_BYTES, FMLA_ERR_ALIGNMENT,
-               "kv_quantize: rows must be 16-byte aligned with a block stride that is a multiple of 16 bytes and at least page_block_size*656");
+                   a->rows_stride_block >= a->page_block_size * row_bytes, FMLA_ERR_ALIGNMENT,
+               "kv_quantize: rows must be 16-byte aligned with a block stride that is a multiple of 16 bytes and at least page_block_size*%lld",
+               (long long)row_bytes);
   DeviceGuard guard(a->device);
   FMLA_REQUIRE(guard.ok, FMLA_ERR_CUDA, "kv_quantize: cannot switch to device %d", a->device);
   const int64_t blocks = (a->n_rows + QUANT_WARPS - 1) / QUANT_WARPS;
   FMLA_REQUIRE(blocks <= 0x7fffffffLL, FMLA_ERR_UNSUPPORTED, "kv_quantize: too many rows for one launch");
-  kv_quantize_kernel<<<(unsigned)blocks, 32 * QUANT_WARPS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<const __nv_bfloat16*>(a->kv), a->kv_stride_row, static_cast<uint8_t*>(a->rows), a->page_block_size,
-      a->rows_stride_block, a->n_rows, a->layout);
+  if (m1)
+    kv_quantize_model1_kernel<<<(unsigned)blocks, 32 * QUANT_WARPS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const __nv_bfloat16*>(a->kv), a->kv_stride_row, static_cast<uint8_t*>(a->rows), a->page_block_size,
+        a->rows_stride_block, a->n_rows);
+  else
+    kv_quantize_kernel<<<(unsigned)blocks, 32 * QUANT_WARPS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const __nv_bfloat16*>(a->kv), a->kv_stride_row, static_cast<uint8_t*>(a->rows), a->page_block_size,
+        a->rows_stride_block, a->n_rows, a->layout);
   FMLA_CUDA(cudaGetLastError());
   return FMLA_OK;
 }

@@ -17,6 +17,8 @@
 // out by 1/(1+exp(sink-lse)) without touching lse.
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace fmla {
@@ -49,9 +51,27 @@ struct Bf16Rows {
   const __nv_bfloat16* base;
   int64_t stride;         // elements
   int64_t total_rows;
+  int chunks;             // 16-byte chunks per row: 72 (d_qk = 576) or 64 (d_qk = 512; the row is zero-padded to 576 in shared memory)
   __device__ __forceinline__ bool in_range(int idx) const { return idx >= 0 && idx < total_rows; }
   __device__ __forceinline__ const __nv_bfloat16* row(int idx) const { return base + idx * stride; }
 };
+
+// MODEL1 cache blocks (tests/quant.py:55-75 of the reference): [page x (448 e4m3 | 64 bf16)] [page x (7 e8m0 | pad)].
+struct PagedModel1Rows {
+  const uint8_t* base;
+  int64_t block_stride;   // bytes
+  int page;
+  int64_t total_rows;
+  __device__ __forceinline__ bool in_range(int idx) const { return idx >= 0 && idx < total_rows; }
+};
+
+template <class Rows> __device__ __forceinline__ Rows make_paged_rows(const void* base, int64_t block_stride, int64_t page, int64_t blocks, int layout);
+template <> __device__ __forceinline__ PagedFp8Rows make_paged_rows<PagedFp8Rows>(const void* base, int64_t block_stride, int64_t page, int64_t blocks, int layout) {
+  return PagedFp8Rows{reinterpret_cast<const uint8_t*>(base), block_stride, (int)page, blocks * page, layout};
+}
+template <> __device__ __forceinline__ PagedModel1Rows make_paged_rows<PagedModel1Rows>(const void* base, int64_t block_stride, int64_t page, int64_t blocks, int) {
+  return PagedModel1Rows{reinterpret_cast<const uint8_t*>(base), block_stride, (int)page, blocks * page};
+}
 
 // Dequantises 16 fp8 values (one uint4) with one scale into 8 bf16x2 words.
 __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint32_t* dst /*8 words, 16-B aligned*/) {
@@ -99,7 +119,30 @@ __device__ __forceinline__ void load_row(const Bf16Rows& src, int idx, bool vali
     return;
   }
   const __nv_bfloat16* r = src.row(idx);
-  for (int c = sub; c < 72; c += nsub) *reinterpret_cast<uint4*>(dst + 4 * c) = ldg_nc_16(r + 8 * c);
+  for (int c = sub; c < 72; c += nsub)
+    *reinterpret_cast<uint4*>(dst + 4 * c) = c < src.chunks ? ldg_nc_16(r + 8 * c) : make_uint4(0, 0, 0, 0);
+}
+
+// A MODEL1 row as 512 values (448 dequantised exactly as tests/quant.py:106-118 does: e4m3 times a power-of-two
+// e8m0 scale in bf16, which is exact; then the 64 RoPE values), zero-padded to the 576-wide shared-memory row.
+__device__ __forceinline__ void load_row(const PagedModel1Rows& src, int idx, bool valid, uint32_t* dst, int sub, int nsub) {
+  if (!valid) {
+    for (int c = sub; c < 72; c += nsub) *reinterpret_cast<uint4*>(dst + 4 * c) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int blk = idx / src.page, off = idx - blk * src.page;
+  const uint8_t* block = src.base + blk * src.block_stride;
+  const uint8_t* r = block + (int64_t)off * M1_DATA_BYTES;
+  const uint2 sc = *reinterpret_cast<const uint2*>(block + (int64_t)src.page * M1_DATA_BYTES + 8 * off);
+  for (int c = sub; c < 28; c += nsub) {       // 28 chunks of 16 fp8; one scale byte per 64 values = 4 chunks
+    const int k = c >> 2;
+    const float scale = e8m0_to_float(((k < 4 ? sc.x : sc.y) >> (8 * (k & 3))) & 0xffu);
+    dequant16(ldg_nc_16(r + 16 * c), scale, dst + 8 * c);
+  }
+  for (int c = sub; c < 8; c += nsub)          // 64 bf16 RoPE values = dims 448 .. 511
+    *reinterpret_cast<uint4*>(dst + 224 + 4 * c) = ldg_nc_16(r + M1_D_NOPE + 16 * c);
+  for (int c = sub; c < 8; c += nsub)          // padding up to 576
+    *reinterpret_cast<uint4*>(dst + 256 + 4 * c) = make_uint4(0, 0, 0, 0);
 }
 
 __device__ __forceinline__ float dot_words(const uint4& a, const uint4& b, float acc) {
@@ -124,11 +167,12 @@ struct FwdSmem {
 };
 
 // Loads the bf16 query rows of this head group (rows beyond h_q are zero).
-__device__ __forceinline__ void load_q_group(uint32_t* q_s, const __nv_bfloat16* q, int64_t stride_h, int head0, int h_q) {
+// `chunks` = 16-byte chunks per query row (72, or 64 for d_qk = 512: the rest of the 576-wide row is zero).
+__device__ __forceinline__ void load_q_group(uint32_t* q_s, const __nv_bfloat16* q, int64_t stride_h, int head0, int h_q, int chunks = 72) {
   for (int i = threadIdx.x; i < HG * 72; i += THREADS) {
     const int h = i / 72, c = i % 72;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (head0 + h < h_q) v = ldg_nc_16(q + (head0 + h) * stride_h + 8 * c);
+    if (head0 + h < h_q && c < chunks) v = ldg_nc_16(q + (head0 + h) * stride_h + 8 * c);
     *reinterpret_cast<uint4*>(q_s + h * Q_W + 4 * c) = v;
   }
 }
@@ -250,16 +294,17 @@ __device__ __forceinline__ float final_scale(float m, float l, const float* attn
 // ---------------------------------------------------------------------------------------------
 // Decode
 // ---------------------------------------------------------------------------------------------
+template <class Rows>
 __global__ void __launch_bounds__(THREADS)
 decode_kernel(const FmlaDecodeArgs a, int block_topk) {
+  constexpr int q_chunks = std::is_same<Rows, PagedModel1Rows>::value ? 64 : 72;     // MODEL1: d_qk = 512
   extern __shared__ __align__(16) uint8_t smem_raw[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int part = blockIdx.x, sq = blockIdx.y, head0 = blockIdx.z * HG;
   const SchedRecord rec = reinterpret_cast<const SchedRecord*>(a.sched_meta)[part];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the combine kernel may start launching; it waits for this grid itself
   if (rec.begin_req >= a.b) return;
-  const PagedFp8Rows rows{reinterpret_cast<const uint8_t*>(a.kv), a.kv_stride_block, (int)a.page_block_size,
-                          a.num_blocks * a.page_block_size, a.layout};
+  const Rows rows = make_paged_rows<Rows>(a.kv, a.kv_stride_block, a.page_block_size, a.num_blocks, a.layout);
   const float scale_log2 = a.sm_scale * LOG2E;
   const int tid = threadIdx.x, h = tid >> 4, g = tid & 15, head = head0 + h;
   float acc[32];
@@ -285,13 +330,12 @@ decode_kernel(const FmlaDecodeArgs a, int block_topk) {
     __syncthreads();
     reset_state(s, acc);
     load_q_group(s.q, reinterpret_cast<const __nv_bfloat16*>(a.q) + req * a.q_stride_b + sq * a.q_stride_s,
-                 a.q_stride_h, head0, a.h_q);
+                 a.q_stride_h, head0, a.h_q, q_chunks);
     __syncthreads();
     if (tok_lo < min(tok_hi, main_end))
       attend(s, rows, a.indices + req * a.idx_stride_b + sq * a.idx_stride_s, tok_lo, min(tok_hi, main_end), limit, scale_log2, acc);
     if (tok_hi > main_end) {
-      const PagedFp8Rows extra_rows{reinterpret_cast<const uint8_t*>(a.extra_kv), a.extra_kv_stride_block, (int)a.extra_page_block_size,
-                                    a.extra_num_blocks * a.extra_page_block_size, a.layout};
+      const Rows extra_rows = make_paged_rows<Rows>(a.extra_kv, a.extra_kv_stride_block, a.extra_page_block_size, a.extra_num_blocks, a.layout);
       attend(s, extra_rows, a.extra_indices + req * a.extra_idx_stride_b + sq * a.extra_idx_stride_s, max(tok_lo, main_end) - main_end,
              tok_hi - main_end, extra_len, scale_log2, acc);
     }
@@ -328,11 +372,12 @@ prefill_fwd_kernel(const FmlaPrefillArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int qi = blockIdx.x, head0 = blockIdx.y * HG;
-  const Bf16Rows rows{reinterpret_cast<const __nv_bfloat16*>(a.kv), a.kv_stride_s, a.s_kv};
+  const int chunks = a.d_qk == M1_D_QK ? 64 : 72;
+  const Bf16Rows rows{reinterpret_cast<const __nv_bfloat16*>(a.kv), a.kv_stride_s, a.s_kv, chunks};
   const int tid = threadIdx.x, h = tid >> 4, g = tid & 15, head = head0 + h;
   float acc[32];
   reset_state(s, acc);
-  load_q_group(s.q, reinterpret_cast<const __nv_bfloat16*>(a.q) + qi * a.q_stride_s, a.q_stride_h, head0, a.h_q);
+  load_q_group(s.q, reinterpret_cast<const __nv_bfloat16*>(a.q) + qi * a.q_stride_s, a.q_stride_h, head0, a.h_q, chunks);
   __syncthreads();
   int limit = a.topk_length ? __ldg(a.topk_length + qi) : a.topk;
   limit = max(0, min(limit, a.topk));
@@ -428,7 +473,7 @@ prefill_bwd_dq_kernel(const FmlaPrefillBwdArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int qi = blockIdx.x, head0 = blockIdx.y * HG;
-  const Bf16Rows rows{reinterpret_cast<const __nv_bfloat16*>(a.kv), a.kv_stride_s, a.s_kv};
+  const Bf16Rows rows{reinterpret_cast<const __nv_bfloat16*>(a.kv), a.kv_stride_s, a.s_kv, 72};
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   load_group_q_do(s, a, qi, head0);
   int limit = a.topk_length ? __ldg(a.topk_length + qi) : a.topk;
@@ -492,7 +537,7 @@ prefill_bwd_dkv_kernel(const FmlaPrefillBwdArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int qi = blockIdx.x;
-  const Bf16Rows rows{reinterpret_cast<const __nv_bfloat16*>(a.kv), a.kv_stride_s, a.s_kv};
+  const Bf16Rows rows{reinterpret_cast<const __nv_bfloat16*>(a.kv), a.kv_stride_s, a.s_kv, 72};
   const int tid = threadIdx.x;
   int limit = a.topk_length ? __ldg(a.topk_length + qi) : a.topk;
   limit = max(0, min(limit, a.topk));
@@ -587,9 +632,14 @@ static int set_smem(K kernel, size_t bytes) {
 int launch_simt_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   int plan_parts, overhead, block;
   if (int rc = fmla_decode_plan(a.device, a.h_q, a.s_q, FMLA_KERNEL_SIMT, &plan_parts, &overhead, &block)) return rc;
-  if (int rc = set_smem(simt::decode_kernel, sizeof(simt::FwdSmem))) return rc;
   dim3 grid(a.num_sm_parts, a.s_q, (a.h_q + simt::HG - 1) / simt::HG);
-  simt::decode_kernel<<<grid, simt::THREADS, sizeof(simt::FwdSmem), stream>>>(a, block);
+  if (a.layout == FMLA_LAYOUT_MODEL1) {
+    if (int rc = set_smem(simt::decode_kernel<simt::PagedModel1Rows>, sizeof(simt::FwdSmem))) return rc;
+    simt::decode_kernel<simt::PagedModel1Rows><<<grid, simt::THREADS, sizeof(simt::FwdSmem), stream>>>(a, block);
+  } else {
+    if (int rc = set_smem(simt::decode_kernel<simt::PagedFp8Rows>, sizeof(simt::FwdSmem))) return rc;
+    simt::decode_kernel<simt::PagedFp8Rows><<<grid, simt::THREADS, sizeof(simt::FwdSmem), stream>>>(a, block);
+  }
   FMLA_CUDA(cudaGetLastError());
   return FMLA_OK;
 }

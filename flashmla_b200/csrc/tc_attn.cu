@@ -145,6 +145,7 @@ struct Params {
   const int* extra_topk_length;
   int mode;                      // 0 decode, 1 prefill
   int h_q, topk;
+  int d_qk;                      // values per q / kv row: 576, or 512 (prefill only; the missing RoPE part reads as zero)
   float scale_log2;
   const __nv_bfloat16* q;
   int64_t q_stride0, q_stride1, q_stride_h;   // decode: batch, s_q; prefill: query, unused
@@ -712,8 +713,11 @@ __device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const I
     for (int k = 0; k < 8; ++k) a[k] = ldg_nc_16(nope + 8 * k);
 #pragma unroll
     for (int k = 0; k < 8; ++k) b[k] = ldg_nc_16(nope + 64 + 8 * k);
-    e[0] = ldg_nc_16(rope);
-    e[1] = ldg_nc_16(rope + 8);
+    e[0] = e[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (p.d_qk == D_QK) {     // rows of 512 values end here: their RoPE part reads as zero
+      e[0] = ldg_nc_16(rope);
+      e[1] = ldg_nc_16(rope + 8);
+    }
   } else {      // a head of the padding of a 64-head group: zeros
 #pragma unroll
     for (int k = 0; k < 8; ++k) a[k] = b[k] = make_uint4(0u, 0u, 0u, 0u);
@@ -812,7 +816,7 @@ __device__ __forceinline__ void prefetch_q(const P& p, const Item& it, int head,
   const __nv_bfloat16* nope = row + 256 * half + 128 * g;
   asm volatile("prefetch.global.L2 [%0];" ::"l"(nope));
   asm volatile("prefetch.global.L2 [%0];" ::"l"(nope + 64));
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(row + 512 + 32 * half + 16 * g));
+  if (p.d_qk == D_QK) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + 512 + 32 * half + 16 * g));
 }
 
 template <class P>
@@ -1132,9 +1136,9 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
 // q viewed as (576, h_q, n1, n2) with element strides; box = box_cols dims x 64 heads.  Returns false if the driver
 // refuses the strides (the kernel then reads Q with plain loads).
 static bool make_q_map(CUtensorMap* map, const void* q, int h_q, uint64_t n1, uint64_t n2, int64_t stride_h, int64_t stride1,
-                       int64_t stride2, uint32_t box_cols, CUtensorMapSwizzle swizzle) {
+                       int64_t stride2, uint32_t box_cols, CUtensorMapSwizzle swizzle, int d_qk = D_QK) {
   if (stride_h <= 0 || stride1 <= 0 || stride2 <= 0) return false;
-  const uint64_t dims[4] = {576, (uint64_t)h_q, n1, n2};
+  const uint64_t dims[4] = {(uint64_t)d_qk, (uint64_t)h_q, n1, n2};
   const uint64_t strides[3] = {(uint64_t)stride_h * 2, (uint64_t)stride1 * 2, (uint64_t)stride2 * 2};
   const uint32_t box[4] = {box_cols, 64, 1, 1};
   return tmap::encode(map, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, swizzle) == 0;
@@ -1206,6 +1210,7 @@ bool tc_decode_supported(const FmlaDecodeArgs& a) {
   auto pool_ok = [](int64_t stride, int64_t blocks, int64_t page) {
     return stride % ROW_BYTES == 0 && (uint64_t)(blocks - 1) * (uint64_t)(stride / ROW_BYTES) + (uint64_t)page <= 0x7fffffffull;
   };
+  if (a.layout == FMLA_LAYOUT_MODEL1) return false;      // the 584-byte block-wise format runs on the CUDA-core kernel
   if (!(a.sm_scale > 0.f) || !pool_ok(a.kv_stride_block, a.num_blocks, a.page_block_size)) return false;
   return a.extra_kv == nullptr || pool_ok(a.extra_kv_stride_block, a.extra_num_blocks, a.extra_page_block_size);
 }
@@ -1213,6 +1218,7 @@ bool tc_decode_supported(const FmlaDecodeArgs& a) {
 int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   tc::Params p = {};
   p.mode = 0;
+  p.d_qk = D_QK;
   p.h_q = a.h_q; p.topk = a.topk;
   FMLA_REQUIRE(a.sm_scale > 0.f, FMLA_ERR_UNSUPPORTED, "the tensor-core kernel needs a positive softmax scale (got %g); use FMLA_KERNEL_SIMT", (double)a.sm_scale);
   p.scale_log2 = a.sm_scale * LOG2E;
@@ -1268,7 +1274,12 @@ int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.sm_scale * LOG2E;
   p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
   p.q_stride0 = a.q_stride_s; p.q_stride1 = 0; p.q_stride_h = a.q_stride_h;
-  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  // d_qk = 512: q and kv rows hold 512 values and V is all of them.  The maps are made over 512 columns and the TMA
+  // unit zero-fills what lies beyond, so the kernel sees 576-wide rows whose last 64 features are zero: the first 512
+  // features of a row are V either way, and zero features add nothing to q . k.
+  const int d_qk = a.d_qk == 0 ? D_QK : a.d_qk;
+  p.d_qk = d_qk;
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 64, CU_TENSOR_MAP_SWIZZLE_128B, d_qk);
   p.indices = a.indices; p.idx_stride0 = a.idx_stride_s; p.idx_stride1 = 0;
   p.topk_length = a.topk_length; p.attn_sink = a.attn_sink;
   p.kv_bf16 = reinterpret_cast<const __nv_bfloat16*>(a.kv);
@@ -1276,8 +1287,8 @@ int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream) {
   p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
   p.lse = a.lse; p.max_logits = a.max_logits;
   p.status = a.status;
-  if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_QK, (uint64_t)a.s_kv, (uint64_t)a.kv_stride_s * 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_QK, (uint64_t)a.s_kv, (uint64_t)a.kv_stride_s * 2, 32, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
+  if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_qk, (uint64_t)a.s_kv, (uint64_t)a.kv_stride_s * 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_qk, (uint64_t)a.s_kv, (uint64_t)a.kv_stride_s * 2, 32, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
   const int groups = (a.h_q + 127) / 128;
   int clusters = sm_count() / 2 / groups;
   if (clusters < 1) clusters = 1;

@@ -3,8 +3,10 @@ flash_mla/flash_mla_interface.py:8-211 (same names, argument order, defaults, re
 assertion behaviour) on top of the C ABI in include/flashmla_b200.h.
 
 Differences from the reference, all additive:
-  * ``flash_mla_with_kvcache`` takes a keyword-only ``kvcache_layout`` ("v32" default, or
-    "mxfp8_e8m0_32" for rows with one e8m0 scale per 32 elements; both are 656 bytes per token).
+  * ``flash_mla_with_kvcache`` takes a keyword-only ``kvcache_layout``.  Left out, the format follows the query
+    width like the reference's dispatch (csrc/api/sparse_decode.h:318-325): d_qk = 576 means "v32" (656 bytes per
+    token), d_qk = 512 means "model1" (584 bytes per token, stored block-wise).  "mxfp8_e8m0_32" selects rows with
+    one e8m0 scale per 32 elements (656 bytes per token, d_qk = 576), a format the reference does not have.
   * ``flash_mla_with_kvcache`` takes a keyword-only ``attn_done_event`` (a timing event recorded
     between its two kernels).
   * ``flash_mla_sparse_bwd`` and ``SparseMLAFunction`` provide the backward of the sparse prefill.
@@ -24,7 +26,8 @@ import torch
 from . import _lib
 
 D_QK, D_V, ROW_BYTES = 576, 512, 656
-_LAYOUTS = {None: _lib.LAYOUT_V32, "v32": _lib.LAYOUT_V32, "mxfp8_e8m0_32": _lib.LAYOUT_MXFP8}
+M1_D_QK, M1_ROW_BYTES = 512, 584        # the MODEL1 cache format (d_qk = 512; tests/quant.py:55-75 of the reference)
+_LAYOUTS = {None: _lib.LAYOUT_V32, "v32": _lib.LAYOUT_V32, "mxfp8_e8m0_32": _lib.LAYOUT_MXFP8, "model1": _lib.LAYOUT_MODEL1}
 _KERNELS = {"auto": _lib.KERNEL_AUTO, "simt": _lib.KERNEL_SIMT, "tc": _lib.KERNEL_TC}
 
 
@@ -134,7 +137,8 @@ def flash_mla_with_kvcache(
     """Sparse MLA decode over a paged FP8 KV cache (flash_mla_interface.py:53-173 of the reference).
 
     q: (b, s_q, h_q, 576) bf16.  k_cache: (num_blocks, page_block_size, 1, 656) bytes (fp8/uint8/int8);
-    the block stride may exceed page_block_size*656.  indices: (b, s_q, topk) int32 with
+    the block stride may exceed page_block_size*656.  With q (b, s_q, h_q, 512) the cache is the reference's MODEL1
+    format, (num_blocks, page_block_size, 1, 584) as tests/quant.py:55-75 lays it out.  indices: (b, s_q, topk) int32 with
     indices[i,j,k] = page_index*page_block_size + offset_in_page, or -1.  attn_sink: (h_q,) fp32.
     topk_length: (b,) int32, only the leftmost topk_length[i] slots are attended.
     attn_done_event: an optional timing event, recorded between the attention and the combine kernel.
@@ -195,15 +199,20 @@ def flash_mla_with_kvcache(
     b, s_q, h_q, d_qk = q.shape
     if q.dtype != torch.bfloat16:
         raise RuntimeError("q must be bfloat16")
-    if d_qk != D_QK or head_dim_v != D_V:
-        raise RuntimeError(f"only head_dim 576 with head_dim_v 512 is supported (got {d_qk}, {head_dim_v})")
+    if d_qk not in (D_QK, M1_D_QK) or head_dim_v != D_V:
+        raise RuntimeError(f"only head_dim 576 or 512 with head_dim_v 512 is supported (got {d_qk}, {head_dim_v})")
+    if kvcache_layout is None and d_qk == M1_D_QK:
+        kvcache_layout = "model1"
+    if (_LAYOUTS[kvcache_layout] == _lib.LAYOUT_MODEL1) != (d_qk == M1_D_QK):
+        raise RuntimeError(f"kvcache_layout {kvcache_layout!r} does not go with head_dim {d_qk}")
+    ROW = M1_ROW_BYTES if d_qk == M1_D_QK else ROW_BYTES
     if k_cache.element_size() != 1:
         raise RuntimeError("k_cache must have a 1-byte dtype (float8_e4m3fn, uint8 or int8)")
     num_blocks, page, h_k, row_bytes = k_cache.shape
-    if h_k != 1 or row_bytes != ROW_BYTES:
-        raise RuntimeError(f"k_cache must be (num_blocks, page_block_size, 1, {ROW_BYTES}); got {tuple(k_cache.shape)}")
-    if k_cache.stride(-1) != 1 or k_cache.stride(1) != ROW_BYTES:
-        raise RuntimeError("k_cache rows must be contiguous 656-byte records (stride(1) == 656)")
+    if h_k != 1 or row_bytes != ROW:
+        raise RuntimeError(f"k_cache must be (num_blocks, page_block_size, 1, {ROW}); got {tuple(k_cache.shape)}")
+    if k_cache.stride(-1) != 1 or k_cache.stride(1) != ROW:
+        raise RuntimeError(f"k_cache rows must be contiguous {ROW}-byte records (stride(1) == {ROW})")
     if indices.dtype != torch.int32 or tuple(indices.shape[:2]) != (b, s_q):
         raise RuntimeError("indices must be int32 of shape (b, s_q, topk)")
     if q.stride(-1) != 1 or indices.stride(-1) != 1:
@@ -217,8 +226,8 @@ def flash_mla_with_kvcache(
         raise RuntimeError("topk_length must be a contiguous int32 tensor of shape (b,)")
     if extra_k_cache is not None:
         if (extra_k_cache.dim() != 4 or extra_k_cache.element_size() != 1 or extra_k_cache.shape[2] != 1
-                or extra_k_cache.shape[3] != ROW_BYTES or extra_k_cache.stride(-1) != 1 or extra_k_cache.stride(1) != ROW_BYTES):
-            raise RuntimeError(f"extra_k_cache must be (num_blocks, page_block_size, 1, {ROW_BYTES}) bytes with contiguous 656-byte rows")
+                or extra_k_cache.shape[3] != ROW or extra_k_cache.stride(-1) != 1 or extra_k_cache.stride(1) != ROW):
+            raise RuntimeError(f"extra_k_cache must be (num_blocks, page_block_size, 1, {ROW}) bytes with contiguous {ROW}-byte rows")
         if (extra_indices_in_kvcache.dtype != torch.int32 or extra_indices_in_kvcache.dim() != 3
                 or tuple(extra_indices_in_kvcache.shape[:2]) != (b, s_q) or extra_indices_in_kvcache.stride(-1) != 1):
             raise RuntimeError("extra_indices_in_kvcache must be int32 of shape (b, s_q, extra_topk) with a contiguous last dimension")
@@ -288,8 +297,8 @@ def _check_prefill(q, kv, indices, d_v, attn_sink, topk_length):
     s_kv, h_kv, _ = kv.shape
     if q.dtype != torch.bfloat16 or kv.dtype != torch.bfloat16 or indices.dtype != torch.int32:
         raise RuntimeError("q and kv must be bfloat16 and indices int32")
-    if d_qk != D_QK or kv.shape[2] != D_QK or d_v != D_V:
-        raise RuntimeError(f"only d_qk=576 with d_v=512 is supported (got {d_qk}, {d_v})")
+    if d_qk not in (D_QK, M1_D_QK) or kv.shape[2] != d_qk or d_v != D_V:
+        raise RuntimeError(f"only d_qk=576 or 512 (q and kv alike) with d_v=512 is supported (got {d_qk}, {kv.shape[2]}, {d_v})")
     if h_kv != 1 or tuple(indices.shape[:2]) != (s_q, 1):
         raise RuntimeError("h_kv must be 1 and indices must be (s_q, 1, topk)")
     if q.stride(-1) != 1 or kv.stride(-1) != 1 or indices.stride(-1) != 1:
@@ -315,7 +324,7 @@ def flash_mla_sparse_fwd(
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Sparse attention prefill forward (flash_mla_interface.py:176-211 of the reference).
 
-    q (s_q, h_q, 576) bf16, kv (s_kv, 1, 576) bf16, indices (s_q, 1, topk) int32 where an index
+    q (s_q, h_q, d_qk) bf16, kv (s_kv, 1, d_qk) bf16 with d_qk = 576 or 512, indices (s_q, 1, topk) int32 where an index
     outside [0, s_kv) is invalid; topk_length (s_q,) keeps only the leftmost slots of each query.
     Returns (out (s_q, h_q, 512) bf16, max_logits (s_q, h_q) fp32, lse (s_q, h_q) fp32).
     """
@@ -332,6 +341,7 @@ def flash_mla_sparse_fwd(
     a.indices, a.idx_stride_s = indices.data_ptr(), indices.stride(0)
     a.attn_sink, a.topk_length = _ptr(attn_sink), _ptr(topk_length)
     a.out, a.max_logits, a.lse, a.status = out.data_ptr(), max_logits.data_ptr(), lse.data_ptr(), _status(dev).data_ptr()
+    a.d_qk = q.shape[-1]
     _lib.check(_lib.load().fmla_sparse_prefill_fwd(C.byref(a), _stream(dev)))
     return out, max_logits, lse
 
@@ -364,6 +374,8 @@ def flash_mla_sparse_bwd(
     a constant.
     """
     s_q, s_kv, h_q, topk = _check_prefill(q, kv, indices, d_v, attn_sink, topk_length)
+    if q.shape[-1] != D_QK:
+        raise RuntimeError("the backward covers d_qk = 576 only")
     dev = q.device
     if out.dtype != torch.bfloat16 or dout.dtype != torch.bfloat16 or tuple(out.shape) != (s_q, h_q, D_V) or tuple(dout.shape) != (s_q, h_q, D_V):
         raise RuntimeError("out and dout must be bfloat16 of shape (s_q, h_q, 512)")

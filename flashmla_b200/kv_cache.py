@@ -12,31 +12,43 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .interface import D_QK, ROW_BYTES, _LAYOUTS, _require_cuda, _stream
+from .interface import D_QK, ROW_BYTES, M1_D_QK, M1_ROW_BYTES, _LAYOUTS, _require_cuda, _stream
 
 
 def quantize_k_cache(kv: torch.Tensor, kvcache_layout: Optional[str] = None, *, out: Optional[torch.Tensor] = None,
                      row_pad: int = 0) -> torch.Tensor:
-    """bf16 (num_blocks, page_block_size, 1, 576) -> bytes (num_blocks, page_block_size, 1, 656).
+    """bf16 (num_blocks, page_block_size, 1, 576) -> bytes (num_blocks, page_block_size, 1, 656), or with the
+    "model1" layout bf16 (.., 512) -> bytes (num_blocks, page_block_size, 1, 584) laid out block-wise.
 
-    ``kvcache_layout``: "v32" (default; 4 fp32 scales per row) or "mxfp8_e8m0_32" (16 e8m0 scale bytes per row).
+    ``kvcache_layout``: "v32" (default for 576 values per row; 4 fp32 scales per row), "mxfp8_e8m0_32" (16 e8m0 scale
+    bytes per row) or "model1" (default for 512 values per row; tests/quant.py:55-75 of the reference: a block is
+    [page x (448 e4m3 | 64 bf16)] followed by [page x (7 e8m0 | pad)], padded to a multiple of 576 bytes).
     ``row_pad`` spare rows per block make the block stride exceed page_block_size*656, as the reference's fixture
     does; ``out`` reuses an existing pool of the right shape.
     """
     _require_cuda(kv, "kv")
-    if kv.dim() != 4 or kv.shape[2] != 1 or kv.shape[3] != D_QK or kv.dtype != torch.bfloat16:
-        raise RuntimeError("kv must be bfloat16 of shape (num_blocks, page_block_size, 1, 576)")
+    if kvcache_layout is None and kv.dim() == 4 and kv.shape[3] == M1_D_QK:
+        kvcache_layout = "model1"
     if kvcache_layout not in _LAYOUTS:
         raise ValueError(f"kvcache_layout must be one of {[k for k in _LAYOUTS if k]}, got {kvcache_layout!r}")
+    m1 = _LAYOUTS[kvcache_layout] == _lib.LAYOUT_MODEL1
+    d, row = (M1_D_QK, M1_ROW_BYTES) if m1 else (D_QK, ROW_BYTES)
+    if kv.dim() != 4 or kv.shape[2] != 1 or kv.shape[3] != d or kv.dtype != torch.bfloat16:
+        raise RuntimeError(f"kv must be bfloat16 of shape (num_blocks, page_block_size, 1, {d})")
     nb, page = kv.shape[0], kv.shape[1]
     kv = kv.contiguous()
     if out is None:
-        pool = torch.zeros((nb, page + row_pad, 1, ROW_BYTES), dtype=torch.uint8, device=kv.device)
-        out = pool[:, :page]
-    elif (out.dtype != torch.uint8 or tuple(out.shape) != (nb, page, 1, ROW_BYTES) or out.device != kv.device
-          or out.stride(1) != ROW_BYTES or out.stride(3) != 1):
-        raise RuntimeError("out must be a uint8 CUDA tensor of shape (num_blocks, page_block_size, 1, 656) with packed rows")
-    a = _lib.KvQuantArgs(kv.device.index, _LAYOUTS[kvcache_layout], nb * page, page, kv.data_ptr(), D_QK,
+        if m1:
+            padded = (page * row + 575) // 576 * 576
+            pool = torch.zeros((nb, padded), dtype=torch.uint8, device=kv.device)
+            out = pool[:, :page * row].view(nb, page, 1, row)
+        else:
+            pool = torch.zeros((nb, page + row_pad, 1, row), dtype=torch.uint8, device=kv.device)
+            out = pool[:, :page]
+    elif (out.dtype != torch.uint8 or tuple(out.shape) != (nb, page, 1, row) or out.device != kv.device
+          or out.stride(1) != row or out.stride(3) != 1):
+        raise RuntimeError(f"out must be a uint8 CUDA tensor of shape (num_blocks, page_block_size, 1, {row}) with packed rows")
+    a = _lib.KvQuantArgs(kv.device.index, _LAYOUTS[kvcache_layout], nb * page, page, kv.data_ptr(), d,
                          out.data_ptr(), out.stride(0))
     _lib.check(_lib.load().fmla_kv_quantize(C.byref(a), _stream(kv.device)))
     return out

@@ -22,11 +22,26 @@ import torch
 D_QK, D_NOPE, D_V, ROW_BYTES = 576, 512, 512, 656
 LAYOUT_V32 = "v32"
 LAYOUT_MXFP8 = "mxfp8_e8m0_32"
+LAYOUT_MODEL1 = "model1"      # d_qk = 512: 448 e4m3 + 64 bf16 per token, 7 e8m0 scales per 64, stored block-wise (584 bytes per token)
 
 
 def quantize_kv_rows(kv: torch.Tensor, layout: str = LAYOUT_V32, row_pad: int = 0) -> torch.Tensor:
     """bf16 [num_blocks, page, 1, 576] -> uint8 [num_blocks, page, 1, 656] (block stride (page+row_pad)*656)."""
     nb, page, hk, d = kv.shape
+    if layout == LAYOUT_MODEL1:
+        # [nb, page, 1, 512] -> [nb, page, 1, 584] viewing blocks [page x (448 e4m3 | 64 bf16)] [page x (7 e8m0 | pad)],
+        # padded to a multiple of 576 bytes like the reference's fixture (tests/quant.py:55-75)
+        assert hk == 1 and d == 512 and kv.dtype == torch.bfloat16 and row_pad == 0
+        x = kv.view(nb, page, d)
+        tiles = x[..., :448].float().view(nb, page, 7, 64)
+        scale = torch.exp2(torch.ceil(torch.log2((tiles.abs().amax(-1) / 448.0).clamp_min(1e-4))))
+        fp8 = (tiles / scale.unsqueeze(-1)).to(torch.float8_e4m3fn).view(nb, page, 448)
+        pool = torch.zeros((nb, (page * 584 + 575) // 576 * 576), dtype=torch.uint8, device=kv.device)
+        data = pool[:, :page * 576].view(nb, page, 576)
+        data[..., :448] = fp8.view(torch.uint8)
+        data[..., 448:] = x[..., 448:].contiguous().view(torch.uint8).view(nb, page, 128)
+        pool[:, page * 576:page * 584].view(nb, page, 8)[..., :7] = (torch.log2(scale).round().to(torch.int32) + 127).to(torch.uint8)
+        return pool[:, :page * 584].view(nb, page, 1, 584)
     assert hk == 1 and d == D_QK and kv.dtype == torch.bfloat16
     tile = 128 if layout == LAYOUT_V32 else 32
     x = kv.view(nb, page, d)
@@ -98,7 +113,7 @@ class DecodeWorkload:
     def algorithmic_bytes(self) -> float:
         b, s_q, h_q, d = self.q.shape
         uniq = int(torch.unique(self.indices).numel()) - int(bool((self.indices < 0).any()))
-        return 2.0 * b * s_q * h_q * d + ROW_BYTES * uniq + 2.0 * b * s_q * h_q * D_V
+        return 2.0 * b * s_q * h_q * d + self.kv_rows.shape[-1] * uniq + 2.0 * b * s_q * h_q * D_V
 
 
 def make_decode_workload(
@@ -117,13 +132,14 @@ def make_decode_workload(
     n_pages = b * pages_per_seq
     block_table = torch.randperm(n_pages, generator=gen, device=device).to(torch.int32).view(b, pages_per_seq)
 
-    q = (torch.randn((b, s_q, h_q, D_QK), generator=gen, device=device) * q_std)
+    d_qk = 512 if layout == LAYOUT_MODEL1 else D_QK
+    q = (torch.randn((b, s_q, h_q, d_qk), generator=gen, device=device) * q_std)
     if clamp is not None:
         q.clamp_(-clamp, clamp)
     q = q.to(torch.bfloat16)
     # A large pool whose bf16 source nobody needs is generated and quantised page chunk by page chunk, so that the
     # fp32 temporaries stay small (the 11 GB pool of the MXFP8 configuration would otherwise need ~100 GB of them).
-    chunked = not keep_bf16 and not poison_unused and n_pages * page * D_QK > (1 << 28)
+    chunked = not keep_bf16 and not poison_unused and n_pages * page * D_QK > (1 << 28) and layout != LAYOUT_MODEL1
     kv = None
     if chunked:
         kv_rows = torch.empty((n_pages, page + row_pad, 1, ROW_BYTES), dtype=torch.uint8, device=device)[:, :page]
@@ -134,7 +150,7 @@ def make_decode_workload(
                 part.clamp_(-clamp, clamp)
             kv_rows[lo:lo + part.shape[0]] = quantize_kv_rows(part.to(torch.bfloat16), layout)
     else:
-        kv = (torch.randn((n_pages, page, 1, D_QK), generator=gen, device=device) * kv_std)
+        kv = (torch.randn((n_pages, page, 1, d_qk), generator=gen, device=device) * kv_std)
         if clamp is not None:
             kv.clamp_(-clamp, clamp)
         kv = kv.to(torch.bfloat16)
@@ -163,14 +179,14 @@ def make_decode_workload(
             used = indices.masked_fill(beyond, -1)
         keep = torch.zeros(n_pages * page, dtype=torch.bool, device=device)
         keep[used[used >= 0].to(torch.int64)] = True
-        kv.view(-1, D_QK)[~keep] = float("nan")
+        kv.view(-1, d_qk)[~keep] = float("nan")
 
     if not chunked:
         kv_rows = quantize_kv_rows(kv, layout, row_pad=row_pad)
     return DecodeWorkload(
         q=q, kv_rows=kv_rows, kv_bf16=kv if keep_bf16 else None, block_table=block_table,
         cache_seqlens=seqlens, positions=positions, indices=indices,
-        sm_scale=float(D_QK ** -0.5) if sm_scale is None else sm_scale, layout=layout,
+        sm_scale=float(d_qk ** -0.5) if sm_scale is None else sm_scale, layout=layout,
         attn_sink=attn_sink, topk_length=topk_length)
 
 
@@ -198,13 +214,13 @@ class PrefillWorkload:
 def make_prefill_workload(
     s_q: int, s_kv: int, h_q: int, topk: int, *, seed: int = 0, device: str = "cpu",
     causal_offset: Optional[int] = None, std: float = 1.0, sm_scale: Optional[float] = None,
-    invalid_pads=(-1,), with_sink: bool = False, with_topk_length: bool = False,
+    invalid_pads=(-1,), with_sink: bool = False, with_topk_length: bool = False, d_qk: int = D_QK,
 ) -> PrefillWorkload:
     """Query i draws ``topk`` distinct positions from [0, causal_offset+i] (or [0, s_kv) when no offset), padded with invalid values."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
-    q = (torch.randn((s_q, h_q, D_QK), generator=gen, device=device) * std).to(torch.bfloat16)
-    kv = (torch.randn((s_kv, 1, D_QK), generator=gen, device=device) * std).to(torch.bfloat16)
+    q = (torch.randn((s_q, h_q, d_qk), generator=gen, device=device) * std).to(torch.bfloat16)
+    kv = (torch.randn((s_kv, 1, d_qk), generator=gen, device=device) * std).to(torch.bfloat16)
     dout = (torch.randn((s_q, h_q, D_V), generator=gen, device=device) * std).to(torch.bfloat16)
     if causal_offset is None:
         limits = torch.full((s_q,), s_kv, dtype=torch.int32, device=device)
@@ -225,5 +241,5 @@ def make_prefill_workload(
     if with_topk_length:
         topk_length = torch.randint(0, topk + 1, (s_q,), generator=gen, device=device, dtype=torch.int32)
     return PrefillWorkload(q=q, kv=kv, indices=idx.view(s_q, 1, topk), dout=dout,
-                           sm_scale=float(D_QK ** -0.5) if sm_scale is None else sm_scale,
+                           sm_scale=float(d_qk ** -0.5) if sm_scale is None else sm_scale,
                            attn_sink=attn_sink, topk_length=topk_length)

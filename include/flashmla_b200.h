@@ -42,9 +42,17 @@ extern "C" {
  */
 #define FMLA_STATUS_CLIPPED 100
 
-/* KV-cache row layouts, 656 bytes per token, d_qk = 576 (512 NoPE + 64 RoPE), one KV head. */
+/* KV-cache layouts, one KV head.  V32 and MXFP8: 656 bytes per token, d_qk = 576 (512 NoPE + 64 RoPE). */
 #define FMLA_LAYOUT_V32    0   /* 512 e4m3 | 4 x fp32 scale (per 128) | 64 bf16   (flash_mla/flash_mla_interface.py:94-98) */
 #define FMLA_LAYOUT_MXFP8  1   /* 512 e4m3 | 16 x e8m0 scale (per 32) | 64 bf16   (no counterpart in the reference) */
+/* MODEL1: d_qk = 512 (448 NoPE + 64 RoPE), 584 bytes per token, stored per cache block as
+ * [page_block_size x (448 e4m3 | 64 bf16)] followed by [page_block_size x (7 e8m0 scales, one per 64 values, | 1 pad byte)]
+ * (tests/quant.py:55-75 of the reference; its decode dispatches on d_qk, csrc/api/sparse_decode.h:318-325).  The
+ * value dimension is still 512: the RoPE part belongs to V. */
+#define FMLA_LAYOUT_MODEL1 2
+#define FMLA_MODEL1_ROW_BYTES   584
+#define FMLA_MODEL1_DATA_BYTES  576   /* the part of a token's bytes that sits in the block's leading array */
+#define FMLA_MODEL1_D_QK        512
 
 #define FMLA_D_QK        576
 #define FMLA_D_V         512
@@ -113,9 +121,9 @@ typedef struct {
   int layout;                    /* FMLA_LAYOUT_* */
   int kernel;                    /* FMLA_KERNEL_* */
   float sm_scale;
-  const void* q;                 /* bf16 [b, s_q, h_q, 576], last dim contiguous */
+  const void* q;                 /* bf16 [b, s_q, h_q, 576] (512 with FMLA_LAYOUT_MODEL1), last dim contiguous */
   int64_t q_stride_b, q_stride_s, q_stride_h;
-  const void* kv;                /* bytes [num_blocks, page_block_size, 656] */
+  const void* kv;                /* bytes [num_blocks, page_block_size, 656] (MODEL1: blocks as described at FMLA_LAYOUT_MODEL1) */
   int64_t num_blocks, page_block_size;
   int64_t kv_stride_block;       /* bytes, multiple of 16 */
   const int32_t* indices;        /* [b, s_q, topk]: block*page_block_size + offset, or -1 */
@@ -173,9 +181,9 @@ typedef struct {
   int s_q, s_kv, h_q, topk;
   int kernel;
   float sm_scale;
-  const void* q;                 /* bf16 [s_q, h_q, 576] */
+  const void* q;                 /* bf16 [s_q, h_q, d_qk] */
   int64_t q_stride_s, q_stride_h;
-  const void* kv;                /* bf16 [s_kv, 1, 576] */
+  const void* kv;                /* bf16 [s_kv, 1, d_qk] */
   int64_t kv_stride_s;           /* elements */
   const int32_t* indices;        /* [s_q, 1, topk]; valid iff 0 <= idx < s_kv */
   int64_t idx_stride_s;
@@ -185,6 +193,8 @@ typedef struct {
   float* max_logits;             /* fp32 [s_q, h_q] */
   float* lse;                    /* fp32 [s_q, h_q] */
   int32_t* status;               /* optional, as in FmlaDecodeArgs */
+  int d_qk;                      /* 576, or 512 (q and kv rows of 512 values; the reference's d_qk = 512 prefill,
+                                    csrc/api/sparse_fwd.h:213-240); 0 means 576 */
 } FmlaPrefillArgs;
 int fmla_sparse_prefill_fwd(const FmlaPrefillArgs* args, void* cuda_stream);
 
@@ -225,7 +235,8 @@ int fmla_sparse_prefill_bwd(const FmlaPrefillBwdArgs* args, void* cuda_stream);
 int64_t fmla_sparse_prefill_bwd_workspace(int s_q, int h_q, int topk, int kernel);
 
 /*
- * KV-cache writer: quantises bf16 rows [576] into 656-byte cache rows of the given layout.  Replaces the torch
+ * KV-cache writer: quantises bf16 rows [576] into 656-byte cache rows of the given layout (FMLA_LAYOUT_MODEL1: rows
+ * [512] into the block-wise 584-byte form, with rows_stride_block >= page_block_size * 584).  Replaces the torch
  * fixture quantize_k_cache (tests/quant.py:20-78; the reference ships no kernel for it) byte for byte for the V32
  * layout; the MXFP8 layout applies the same scale rule per 32 values.  Row i goes to
  * rows + (i / page_block_size) * rows_stride_block + (i % page_block_size) * 656.

@@ -65,15 +65,34 @@ def golden_quant(ref_quant):
         block_table=bits(block_table), positions=bits(pos), cache_rows=bits(rows_idx), page=np.int32(16))
 
 
+def golden_quant_model1(ref_quant):
+    """The reference's MODEL1 quantiser (d_qk = 512, block-wise 584-byte format) on the same kind of inputs."""
+    gen = torch.Generator().manual_seed(12)
+    kv = torch.randn((5, 16, 1, 512), generator=gen)
+    kv[0, 0] *= 1e-6            # exercises the 1e-4 floor of the scale rule
+    kv[1, 3, 0, :64] = 0.0      # an all-zero tile
+    kv[2] *= 37.0
+    kv[3, :, :, 64:128] *= 448.0
+    kv = kv.to(torch.bfloat16)
+    layout = ref_quant.FP8KVCacheLayout.MODEL1_FP8Sparse
+    rows = ref_quant.quantize_k_cache(kv, layout)
+    deq = ref_quant.dequantize_k_cache(rows, layout)
+    # the reference leaves the 8th scale byte of every token uninitialised: it is stored here as zero
+    flat = rows.view(torch.uint8).reshape(5, 16 * 584).clone()
+    flat[:, 16 * 576:].view(5, 16, 8)[..., 7] = 0
+    np.savez_compressed(os.path.join(HERE, "quant_model1.npz"), kv=bits(kv), rows=bits(flat.view(5, 16, 1, 584)), dequant=bits(deq))
+
+
 def golden_decode(ref_lib, ref_quant, ref_ref, name, *, b, s_q, h_q, topk, s_k, seed, invalid_tail=0,
-                  invalid_frac=0.0, with_sink=False, with_topk_length=False, all_invalid_row=False, **dist):
-    w = wl.make_decode_workload(b, s_q, h_q, topk, s_k, s_k, seed=seed, invalid_tail=invalid_tail,
+                  invalid_frac=0.0, with_sink=False, with_topk_length=False, all_invalid_row=False, layout=wl.LAYOUT_V32, **dist):
+    w = wl.make_decode_workload(b, s_q, h_q, topk, s_k, s_k, seed=seed, invalid_tail=invalid_tail, layout=layout,
                                 invalid_frac=invalid_frac, with_sink=with_sink, with_topk_length=with_topk_length, **dist)
     if all_invalid_row:
         w.indices[0, 0, :] = -1
     rows_fp8 = w.kv_rows.view(torch.float8_e4m3fn)
-    deq = ref_quant.dequantize_k_cache(rows_fp8, ref_quant.FP8KVCacheLayout.V32_FP8Sparse)
-    p = ref_lib.TestParam(s_q=s_q, s_kv=s_k, topk=topk, h_q=h_q, h_kv=1, d_qk=576, d_v=512,
+    ref_layout = ref_quant.FP8KVCacheLayout.MODEL1_FP8Sparse if layout == wl.LAYOUT_MODEL1 else ref_quant.FP8KVCacheLayout.V32_FP8Sparse
+    deq = ref_quant.dequantize_k_cache(rows_fp8, ref_layout)
+    p = ref_lib.TestParam(s_q=s_q, s_kv=s_k, topk=topk, h_q=h_q, h_kv=1, d_qk=w.q.shape[-1], d_v=512,
                           decode=ref_lib.ExtraTestParamForDecode(b=b, is_varlen=False, have_zero_seqlen_k=False))
     scope = ref_lib.KVScope(p, w.cache_seqlens, w.block_table, deq, w.positions, w.indices, w.topk_length)
     t = ref_lib.TestcaseForDecode(p, w.q, w.attn_sink, w.sm_scale, scope, None)
@@ -117,14 +136,14 @@ def golden_decode_extra(ref_lib, ref_quant, ref_ref, name, *, b, s_q, h_q, topk,
 
 
 def golden_prefill(ref_lib, ref_ref, name, *, s_q, s_kv, h_q, topk, seed, with_sink=False, with_topk_length=False,
-                   causal_offset=None, sm_scale=None, std=1.0, dead_rows=()):
+                   causal_offset=None, sm_scale=None, std=1.0, dead_rows=(), d_qk=576):
     pads = (-2147483648, -123456, -1, s_kv, 114514, 1919810, 2147480000, 2147483647)
     w = wl.make_prefill_workload(s_q, s_kv, h_q, topk, seed=seed, causal_offset=causal_offset, std=std,
                                  sm_scale=sm_scale, invalid_pads=pads, with_sink=with_sink,
-                                 with_topk_length=with_topk_length)
+                                 with_topk_length=with_topk_length, d_qk=d_qk)
     for r in dead_rows:
         w.indices[r] = 2147483647
-    p = ref_lib.TestParam(s_q=s_q, s_kv=s_kv, topk=topk, h_q=h_q, h_kv=1, d_qk=576, d_v=512)
+    p = ref_lib.TestParam(s_q=s_q, s_kv=s_kv, topk=topk, h_q=h_q, h_kv=1, d_qk=d_qk, d_v=512)
     t = ref_lib.Testcase(p, w.dout, w.q, w.kv, w.indices, w.sm_scale, w.attn_sink, w.topk_length)
     with torch.inference_mode():
         out, out_f32, max_logits, lse = ref_ref.ref_sparse_attn_fwd(p, t)
@@ -161,6 +180,15 @@ def main():
     golden_prefill(ref_lib, ref_ref, "prefill_sink_len", s_q=7, s_kv=96, h_q=8, topk=128, seed=4,
                    with_sink=True, with_topk_length=True, sm_scale=0.5, std=0.1, dead_rows=(2,))
     golden_prefill(ref_lib, ref_ref, "prefill_causal", s_q=5, s_kv=64, h_q=4, topk=64, seed=5, causal_offset=20)
+    # d_qk = 512: the reference's MODEL1 cache format (decode) and its 512-wide prefill
+    golden_quant_model1(ref_quant)
+    golden_decode(ref_lib, ref_quant, ref_ref, "decode_model1", b=3, s_q=2, h_q=16, topk=128, s_k=384, seed=9,
+                  invalid_frac=0.05, with_sink=True, with_topk_length=True, layout=wl.LAYOUT_MODEL1,
+                  q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55)
+    golden_decode(ref_lib, ref_quant, ref_ref, "decode_model1_h128", b=2, s_q=1, h_q=128, topk=192, s_k=512, seed=10,
+                  invalid_frac=0.03, layout=wl.LAYOUT_MODEL1, q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55)
+    golden_prefill(ref_lib, ref_ref, "prefill_d512_h128", s_q=4, s_kv=300, h_q=128, topk=256, seed=13, with_sink=True,
+                   with_topk_length=True, sm_scale=0.5, std=0.1, d_qk=512)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

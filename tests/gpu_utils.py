@@ -15,6 +15,13 @@ def cu(t):
     return None if t is None else t.to(DEV)
 
 
+def cu_strided(t):
+    """Copy of t on the GPU with t's own strides (a padded cache pool keeps its block stride; `.to` would compact it)."""
+    if t is None:
+        return None
+    return torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=DEV).copy_(t)
+
+
 def noncontig(t: torch.Tensor) -> torch.Tensor:
     """Copy of t on the GPU whose leading strides are padded (last dim stays contiguous, padded by
     128 elements so 16-byte alignment is kept), as the reference's fixtures do."""
@@ -28,7 +35,7 @@ def noncontig(t: torch.Tensor) -> torch.Tensor:
 def run_decode(w: wl.DecodeWorkload, sched=None, q=None, indices=None, kv_rows=None):
     sched = sched or flash_mla.get_mla_metadata()[0]
     out, lse = flash_mla.flash_mla_with_kvcache(
-        cu(w.q) if q is None else q, cu(w.kv_rows) if kv_rows is None else kv_rows, None, None, 512, sched, None,
+        cu(w.q) if q is None else q, cu_strided(w.kv_rows) if kv_rows is None else kv_rows, None, None, 512, sched, None,
         w.sm_scale, False, True, cu(w.indices) if indices is None else indices, cu(w.attn_sink), None, None,
         cu(w.topk_length), None, kvcache_layout=w.layout)
     assert flashmla_b200.kernel_status(DEV) == 0, "a kernel reported a timed-out wait"

@@ -10,7 +10,7 @@ import flash_mla
 from flashmla_b200 import _lib, workloads as wl
 from oracle import sched as sched_oracle
 from helpers import bf16, load_golden, t
-from gpu_utils import DEV, cu, noncontig, run_decode, oracle_decode, check_decode
+from gpu_utils import DEV, cu, cu_strided, noncontig, run_decode, oracle_decode, check_decode
 
 pytestmark = pytest.mark.gpu
 
@@ -243,3 +243,46 @@ def test_unsplit_batch_is_complete_for_the_next_kernel_in_the_stream():
         out.zero_()                       # and the one after it, so a late attention kernel would show in `out` too
         torch.cuda.synchronize()
         assert torch.equal(copy, ref)
+
+
+# ---- the reference's d_qk = 512 cache format ("MODEL1": 448 e4m3 + 64 bf16 per token, 7 e8m0 scales per 64 values,
+# ---- stored block-wise; tests/quant.py:55-75 of the reference) ---------------------------------------------------
+@pytest.mark.parametrize("name", ["decode_model1", "decode_model1_h128"])
+def test_model1_golden_reference_outputs(name):
+    g = load_golden(name)
+    out, lse = flash_mla.flash_mla_with_kvcache(
+        cu(bf16(g["q"])), _model1_pool(t(g["kv_rows"])), None, None, 512, flash_mla.get_mla_metadata()[0], None, float(g["sm_scale"]),
+        False, True, cu(t(g["indices"])), cu(t(g["attn_sink"])) if "attn_sink" in g else None, None, None,
+        cu(t(g["topk_length"])) if "topk_length" in g else None)
+    torch.cuda.synchronize()
+    check_decode(out, lse, bf16(g["out"]), t(g["lse"]))
+
+
+def _model1_pool(rows):
+    """A packed (num_blocks, page, 1, 584) fixture on the GPU with blocks padded to a multiple of 576 bytes, as the
+    reference allocates them (tests/quant.py:57-58): the kernels read 16-byte pieces, so blocks start 16-byte aligned."""
+    nb, page = rows.shape[0], rows.shape[1]
+    pool = torch.zeros((nb, (page * 584 + 575) // 576 * 576), dtype=torch.uint8, device=DEV)
+    view = pool[:, :page * 584].view(nb, page, 1, 584)
+    view.copy_(rows)
+    return view
+
+
+M1_CASES = [
+    # b, s_q, h_q, topk, s_lo, s_hi, page, kwargs  (the reference's matrix: d_qk 512 x h_q {64, 128} x pages {2, 64, 69})
+    (4, 1, 64, 64, 512, 512, 2, dict(with_sink=True)),
+    (4, 3, 128, 576, 1024, 1024, 61, dict(invalid_frac=0.02, poison_unused=True)),
+    (3, 2, 128, 2048, 2046, 2046, 64, dict(with_sink=True, with_topk_length=True)),
+    (74, 1, 64, 64, 200, 512, 69, dict(invalid_frac=0.02)),
+    (5, 2, 16, 200, 300, 700, 64, dict(invalid_frac=0.03)),
+]
+
+
+@pytest.mark.parametrize("case", M1_CASES, ids=[f"b{c[0]}sq{c[1]}h{c[2]}k{c[3]}p{c[6]}" for c in M1_CASES])
+def test_model1_against_oracle(case):
+    b, s_q, h_q, topk, lo, hi, page, kw = case
+    w = wl.make_decode_workload(b, s_q, h_q, topk, lo, hi, page=page, layout=wl.LAYOUT_MODEL1, seed=b * 17 + topk,
+                                q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55, **kw)
+    out, lse, _ = run_decode(w)
+    ref_out, ref_lse = oracle_decode(w)
+    check_decode(out, lse, ref_out, ref_lse)

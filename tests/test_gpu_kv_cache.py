@@ -44,6 +44,20 @@ def test_quantiser_matches_the_reference_fixture():
     assert np.array_equal(got.cpu().numpy().reshape(g["rows"].shape), g["rows"])
 
 
+def test_model1_quantiser_matches_the_reference_fixture_and_the_oracle():
+    """The d_qk = 512 block-wise format (tests/quant.py:55-75 of the reference)."""
+    g = load_golden("quant_model1")
+    got = flashmla_b200.quantize_k_cache(bf16(g["kv"]).to(DEV))          # 512 values per row: "model1" by default
+    assert tuple(got.shape) == (5, 16, 1, 584) and got.stride(0) % 576 == 0
+    assert np.array_equal(got.cpu().numpy(), g["rows"])
+    gen = torch.Generator().manual_seed(8)
+    kv = torch.randn((7, 64, 1, 512), generator=gen)
+    kv[2] *= 1e3
+    kv[3, :, :, :64] = 0.0
+    kv = kv.to(torch.bfloat16)
+    assert torch.equal(flashmla_b200.quantize_k_cache(kv.to(DEV), wl.LAYOUT_MODEL1).cpu(), quant.quantize_rows(kv, quant.LAYOUT_MODEL1))
+
+
 def test_cache_indices_are_bit_exact():
     g = load_golden("quant_v32")
     pos, table = torch.from_numpy(g["positions"]), torch.from_numpy(g["block_table"])

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 PADS = (-2147483648, -123456, -1, 114514, 1919810, 2147480000, 2147483647)
 
 
-@pytest.mark.parametrize("name", ["prefill_small", "prefill_sink_len", "prefill_causal", "prefill_h128"])
+@pytest.mark.parametrize("name", ["prefill_small", "prefill_sink_len", "prefill_causal", "prefill_h128", "prefill_d512_h128"])
 def test_golden_reference_outputs(name):
     g = load_golden(name)
     out, mx, lse = flash_mla.flash_mla_sparse_fwd(
@@ -41,10 +41,13 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("d_qk", [576, 512])
 @pytest.mark.parametrize("case", CASES, ids=[f"sq{c[0]}kv{c[1]}h{c[2]}k{c[3]}" for c in CASES])
-def test_forward_against_oracle(case):
+def test_forward_against_oracle(case, d_qk):
+    """d_qk = 512 is the reference's other head dimension (csrc/api/sparse_fwd.h:213-240): q and kv rows of 512 values,
+    all of them V."""
     s_q, s_kv, h_q, topk, kw = case
-    w = wl.make_prefill_workload(s_q, s_kv, h_q, topk, seed=s_q + topk, **kw)
+    w = wl.make_prefill_workload(s_q, s_kv, h_q, topk, seed=s_q + topk, d_qk=d_qk, **kw)
     out, mx, lse = run_prefill(w, q=noncontig(w.q), kv=noncontig(w.kv), indices=noncontig(w.indices))
     ref_out, _, ref_mx, ref_lse = attention.sparse_prefill_fwd(w.q, w.kv, w.indices, w.sm_scale, attn_sink=w.attn_sink,
                                                                topk_length=w.topk_length)

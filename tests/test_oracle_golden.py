@@ -26,6 +26,29 @@ def test_v32_dequant_bit_exact():
     assert np.array_equal(deq.view(torch.int16).numpy().view(np.uint16), g["dequant"])
 
 
+def test_model1_rows_byte_exact_and_dequant_bit_exact():
+    """The reference's d_qk = 512 cache format (tests/quant.py:55-75, :106-118)."""
+    g = load_golden("quant_model1")
+    kv = bf16(g["kv"])
+    rows = quant.quantize_rows(kv, quant.LAYOUT_MODEL1)
+    assert rows.shape == (5, 16, 1, 584) and rows.stride(0) % 576 == 0
+    assert np.array_equal(rows.numpy(), g["rows"])
+    assert np.array_equal(wl.quantize_kv_rows(kv, wl.LAYOUT_MODEL1).numpy(), g["rows"])
+    deq = quant.dequantize_rows(t(g["rows"]), quant.LAYOUT_MODEL1)
+    assert np.array_equal(deq.view(torch.int16).numpy().view(np.uint16), g["dequant"])
+
+
+@pytest.mark.parametrize("name", ["decode_model1", "decode_model1_h128"])
+def test_model1_decode_matches_reference(name):
+    g = load_golden(name)
+    deq = quant.dequantize_rows(t(g["kv_rows"]), quant.LAYOUT_MODEL1)
+    sink = t(g["attn_sink"]) if "attn_sink" in g else None
+    tl = t(g["topk_length"]) if "topk_length" in g else None
+    out, lse, _ = attention.sparse_decode(bf16(g["q"]), deq, t(g["indices"]), float(g["sm_scale"]), attn_sink=sink, topk_length=tl)
+    assert_close("out", out.float(), bf16(g["out"]).float(), abs_tol=1e-6, rel_tol=2.0 ** -7, cos_tol=1e-6)
+    assert_close("lse", lse.contiguous(), t(g["lse"]), abs_tol=1e-5, rel_tol=1e-5, cos_tol=1e-9)
+
+
 def test_index_map_bit_exact():
     g = load_golden("quant_v32")
     got = quant.abs_to_cache_indices(t(g["positions"]), t(g["block_table"]), int(g["page"]))
@@ -58,7 +81,7 @@ def test_decode_with_extra_cache_matches_reference():
     assert_close("lse", lse.contiguous(), t(g["lse"]), abs_tol=1e-5, rel_tol=1e-5, cos_tol=1e-9)
 
 
-@pytest.mark.parametrize("name", ["prefill_small", "prefill_sink_len", "prefill_causal", "prefill_h128"])
+@pytest.mark.parametrize("name", ["prefill_small", "prefill_sink_len", "prefill_causal", "prefill_h128", "prefill_d512_h128"])
 def test_prefill_matches_reference(name):
     g = load_golden(name)
     sink = t(g["attn_sink"]) if "attn_sink" in g else None
