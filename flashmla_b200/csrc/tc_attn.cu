@@ -72,7 +72,7 @@ constexpr int GROWS = 64 / NGW;       // rows of a block fetched by one gather w
 constexpr int QK_WARP = NSW + NPW, PV_WARP = QK_WARP + 2, GATHER_WARP = QK_WARP + 4;
 // decode runs all warps; prefill has no gather warps (24 / 20 warps)
 constexpr int threads_of(int mode) { return 32 * (GATHER_WARP + (mode == 0 ? NGW : 0)); }
-constexpr int NSTAGE_DECODE = 3, NSTAGE_PREFILL = 5, NRAW = 3, MAX_STAGES = 5;
+constexpr int NSTAGE_DECODE = 4, NSTAGE_PREFILL = 5, NRAW = 2, MAX_STAGES = 5;
 constexpr uint32_t PANEL = T * 128;                 // one 128B-swizzled [64 tokens x 64 dims] panel
 constexpr uint32_t ROPE_PANEL = 4 * PANEL;          // offset of the 64B-swizzled [64 x 32] RoPE panel in a stage
 constexpr uint32_t STAGE_BYTES = 4 * PANEL + T * 64;
@@ -118,11 +118,12 @@ constexpr uint32_t SM_MTRUE = SM_MREF + 512;                // float [2 teams][6
 constexpr uint32_t SM_SUM = SM_MAX + 2048;                  // float [4][64]: row sums at the end of a query
 constexpr uint32_t SM_IDX = SM_SUM + 1024;                  // int32 [NPW producer warps][RING][PROWS] / [NGW gather warps][RING][GROWS]
 constexpr uint32_t SM_P = 6144;                             // two P buffers (one per team), 1024-byte aligned
-constexpr uint32_t SM_XCHG = SM_P + 2 * P_BYTES;            // float [2 receiving halves][64 heads][32], chunk-swizzled; also the Q tiles
-constexpr uint32_t SM_QROPE = SM_XCHG + 2 * 64 * 32 * 4;    // Q's RoPE panel (A operand of the RoPE k-steps)
+constexpr uint32_t XCHG_BYTES = 2 * 2 * 32 * 64;           // one of the two halves of the partial-sum exchange (the other half travels through the team's P buffer)
+constexpr uint32_t SM_XCHG = SM_P + 2 * P_BYTES;            // float [2 head ranges][2 receiving halves][32 heads][16], chunk-swizzled; also a Q tile
+constexpr uint32_t SM_QROPE = SM_XCHG + XCHG_BYTES;         // Q's RoPE panel (A operand of the RoPE k-steps)
 constexpr uint32_t SM_STAGE = SM_QROPE + QROPE_BYTES;       // stages, then (decode) the raw ring
 constexpr uint32_t SM_RAW = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
-static_assert(SM_LEAVE + 4 <= SM_MASK && SM_XFLAG + NPW * RING <= SM_MAX && SM_MTRUE + 512 <= SM_SUM && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 &&
+static_assert(XCHG_BYTES == P_BYTES && SM_LEAVE + 4 <= SM_MASK && SM_XFLAG + NPW * RING <= SM_MAX && SM_MTRUE + 512 <= SM_SUM && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 &&
               SM_QROPE % 1024 == 0 && SM_STAGE % 1024 == 0 && STAGE_BYTES % 1024 == 0 && SM_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0 && SM_BAR + 8 * NUM_BARS + 12 <= SM_MASK,
               "shared memory map");
 constexpr uint32_t SMEM_USED_PREFILL = SM_STAGE + NSTAGE_PREFILL * STAGE_BYTES;
@@ -761,8 +762,11 @@ __device__ __forceinline__ void half_sync(int half) { asm volatile("bar.sync %0,
 // has been copied: the caller uses them to run the previous item's epilogue in the shadow of the tiles' latency.
 template <class P, class Pre, class Post>
 __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head0, int h, int half,
-                                           int g, bool issuer, uint32_t& uses, uint32_t& items, uint32_t& qmax, Pre pre, Post post) {
-  const uint32_t buf = c.base + SM_XCHG + 8192u * half;
+                                           int g, bool issuer, uint32_t& uses, uint32_t& items, uint32_t& qmax, int stage_p, int pv_wait,
+                                           Pre pre, Post post) {
+  // tiles of feature half 0 land in the exchange buffer, those of half 1 in P buffer `stage_p`: the one that the query's
+  // last PV product does not read.  Its own last reader is PV product number `pv_wait` (-1: none), long issued by now.
+  const uint32_t buf = half == 0 ? c.base + SM_XCHG : c.base + SM_P + (uint32_t)stage_p * P_BYTES;
   const uint32_t bar = bar_addr(c, QT_FULL + half), bar_rope = bar_addr(c, QR_FULL);
   const int c2 = p.mode == 0 ? it.sq : it.req, c3 = p.mode == 0 ? it.req : 0;
   auto request = [&](int r) {
@@ -778,6 +782,8 @@ __device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item&
     if (half == 0) {
       mbar_expect_tx(bar_rope, QROPE_BYTES);
       tma_tile_4d(c.base + SM_QROPE, &p.map_q, 512, head0, c2, c3, bar_rope);
+    } else if (pv_wait >= 0) {
+      wait(c, PV_DONE + stage_p, (uint32_t)pv_wait >> 1, 46);      // on a time-out the tile waits below end the role
     }
     request(0);
   }
@@ -831,9 +837,16 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   // Exchange buffer: region r (the receiving feature half) holds 64 rows (heads) of 32 floats; the 16-byte chunk k
   // of row h sits at chunk position k ^ (h & 7), which spreads eight consecutive rows over all bank groups.
-  const uint32_t xchg_put = c.base + SM_XCHG + 8192u * (1 - half) + 128u * h;
-  const uint32_t xchg_get = c.base + SM_XCHG + 8192u * half + 128u * h;
-  const uint32_t xsw = (uint32_t)h & 7u;
+  // The 32 partial sums a thread hands to its mate travel in two halves of 16: one through the exchange buffer and
+  // one through the team's own P buffer, which is idle until the block's probabilities are written.  Both are laid out
+  // as [head range h / 32][receiving half][32 heads][16 floats]: the 4 KB of a head range are exactly the P rows of the
+  // same 32 heads, so only the two warps of a pair ever touch them, in the exchange as well as when P is written.  The
+  // 16-byte chunk k of a 64-byte row sits at chunk position k ^ ((row / 2) % 4): eight consecutive rows then cover all
+  // bank groups.
+  const uint32_t xoff = 4096u * (uint32_t)(h >> 5) + 64u * (uint32_t)(h & 31);
+  const uint32_t xput = 2048u * (uint32_t)(1 - half) + xoff, xget = 2048u * (uint32_t)half + xoff;
+  const uint32_t xsw = ((uint32_t)h >> 1) & 3u;
+  const uint32_t pbuf = c.base + SM_P + team * P_BYTES, xbuf = c.base + SM_XCHG;
   const uint32_t max_mine = c.base + SM_MAX + 4u * (64 * slot + h), max_mate = c.base + SM_MAX + 4u * (64 * (slot ^ 1) + h);
   const uint32_t mref_mine = c.base + SM_MREF + 4u * (64 * team + h), mref_other = c.base + SM_MREF + 4u * (64 * (team ^ 1) + h);
   const uint32_t sum_base = c.base + SM_SUM + 4u * h, mtrue_base = c.base + SM_MTRUE + 4u * h;
@@ -849,7 +862,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   uint32_t q_absmax = 0;                     // decode: largest |q| of the NoPE part seen by this thread (Q is staged in fp16)
   if (have) {
     if (p.q_tma) {
-      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
+      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, 1, -1, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
     } else {
       load_q_to_tmem(p, c, it, tmem_lane, head, h, half, g, q_absmax);
     }
@@ -868,6 +881,9 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       bool ok = wait(c, S_FULL + team, seq >> 1, 41);
       // the other team has finished with the exchange buffer and has settled the reference maximum of block seq - 1
       ok = ok && (seq == 0 || wait(c, DEC + (team ^ 1), (seq - 1) >> 1, 42));
+      // the PV product that read this team's P buffer last has completed (it did so about a block ago): the buffer
+      // carries half of the exchange now and the block's probabilities later
+      ok = ok && (seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45));
       if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
       tc_fence_after_sync();
       // of the block's 64 tokens this thread finishes 32 (tokens 32*half ..): it reads its own partial dot
@@ -879,7 +895,8 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          st_shared16(xchg_put + (((uint32_t)k ^ xsw) << 4), make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
+          st_shared16((k < 4 ? xbuf : pbuf) + xput + (((uint32_t)(k & 3) ^ xsw) << 4),
+                      make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
       }
       tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * half, keep);
       tmem_ld_wait();
@@ -890,7 +907,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       float x[32];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint4 t = lds_16(xchg_get + (((uint32_t)k ^ xsw) << 4));
+        const uint4 t = lds_16((k < 4 ? xbuf : pbuf) + xget + (((uint32_t)(k & 3) ^ xsw) << 4));
         x[4 * k] = __uint_as_float(keep[4 * k]) + __uint_as_float(t.x);
         x[4 * k + 1] = __uint_as_float(keep[4 * k + 1]) + __uint_as_float(t.y);
         x[4 * k + 2] = __uint_as_float(keep[4 * k + 2]) + __uint_as_float(t.z);
@@ -920,10 +937,9 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_addr(c, DEC + team));
       if (__any_sync(0xffffffffu, bump && alpha != 0.f)) {   // rescale this lane's 256 columns of O
-        // every PV product issued so far must have completed; this team's previous one first, so that the
-        // parity of the other team's barrier cannot be mistaken for the completion before
-        ok = seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 43);
-        ok = ok && wait(c, PV_DONE + (team ^ 1), (seq - 1) >> 1, 44);
+        // every PV product issued so far must have completed (this team's previous one has, see the top of the
+        // block, so the parity of the other team's barrier cannot be mistaken for the completion before)
+        ok = wait(c, PV_DONE + (team ^ 1), (seq - 1) >> 1, 44);
         if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
         tc_fence_after_sync();
 #pragma unroll 1
@@ -952,11 +968,8 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       }
       l_sum += sum;
 
-      if (seq >= 2) {                                      // the PV product that read this team's P buffer last
-        ok = wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
-        if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
-      }
-      const uint32_t pbuf = c.base + SM_P + team * P_BYTES;
+      // P rows of these 32 heads overwrite the pair's exchange data in the buffer: the pair barrier above (row maxima)
+      // lies between the mate's reads of that data and these stores
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         st_shared16(pbuf + swz(h, 4 * half + k), make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]));
@@ -1031,7 +1044,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     // With the TMA path the epilogue's four chunks run between the Q tiles, in the shadow of their latency;
     // either way the next item's first QK^T overlaps the rest of the epilogue.
     if (have_next && p.q_tma) {
-      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
+      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, (int)((last ^ 1u) & 1u), (int)last - 1, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(c, Q_FULL);
