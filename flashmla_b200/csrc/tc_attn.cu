@@ -5,40 +5,50 @@
 // 64 heads runs with its upper half padded by zero queries): CTA r keeps heads [64r, 64r+64) and, of every
 // gathered KV row, only one half of the feature dimension:
 //     half 0 = NoPE[0:256]   + RoPE[0:32],     half 1 = NoPE[256:512] + RoPE[32:64]   (288 dims each)
-// so every row is fetched and dequantised exactly once per pair.  Per block of T = 64 token slots:
+// so every row is fetched and dequantised exactly once per pair.  Work is cut into blocks of T = 64 token slots, and a
+// block passes through these roles (warps per CTA):
 //
-//   prefill producers (8 warps)  warp w owns tokens [8w, 8w+8): indices prefetched into a shared-memory ring by
+//   prefill producers (8)    warp w owns tokens [8w, 8w+8): indices prefetched into a shared-memory ring by
 //                            cp.async, rows gathered with cp.async.bulk.tensor tile::gather4 (four rows per
 //                            instruction, one instruction per lane) straight into the stage: four 128B-swizzled
 //                            NoPE panels [64 tokens x 64 dims] and one 64B-swizzled RoPE panel [64 x 32].  An
 //                            invalid slot gets row coordinate -1, which the TMA unit zero-fills.  The gathers
 //                            signal the leader CTA's stage barrier themselves.
-//   decode gather (2 warps)  warp g fetches rows [32g, 32g+32) into a three-slot raw ring: per four rows one
-//                            256-byte piece (this CTA's NoPE half) and one 144-byte piece (scales + RoPE).
-//   decode convert (8 warps) each dequantises eight rows of the raw slot into the stage: e4m3x2 -> f16x2 (one
+//   decode gather (4)        warp g fetches rows [16g, 16g+16) into a two-slot raw ring: per four rows one gather of
+//                            256 bytes a row (this CTA's NoPE half), one of 64 (its RoPE half) and one of 16 (scales).
+//   decode convert (8)       each dequantises eight rows of the raw slot into the stage: e4m3x2 -> f16x2 (one
 //                            cvt, exact) times the tile scale as f16x2.  Every e4m3 value times a power-of-two
 //                            scale up to 2^7 is exact in fp16 (|x| <= 448 * 128 = 57344 < 65504); larger scales
-//                            saturate at 2^7 (only clips rows whose amax exceeds 57344).  RoPE stays bf16.
-//   QK^T  (1 thread, CTA 0)  18 x tcgen05.mma M=128 N=128 K=16, A = Q from tensor memory, B = the stage
-//                            (K-major); the 16 NoPE k-steps run f16 x f16 in decode (Q is converted once per
-//                            item), bf16 x bf16 in prefill, the 2 RoPE k-steps always bf16 x bf16.  N-half 0 comes
-//                            from CTA 0's stage (feature half 0), N-half 1 from CTA 1's (half 1); the A operand is
-//                            lane-local, TMEM lanes 0-63 hold Q[:, half 0] and lanes 64-127 hold Q[:, half 1], so
-//                            lanes 0-63 / 64-127 of the accumulator receive the two partial dot products of the
-//                            same 64 heads x 64 tokens.
-//   softmax (8 warps/CTA)    the four threads of a head (two feature halves x two groups of 32 tokens) add the
-//                            partials through shared memory, apply the validity mask, run the online softmax in
-//                            base 2 with a lazily updated reference maximum and write P (f16 in decode, bf16 in
-//                            prefill) as the A operand of PV.  They also move each query's Q into tensor memory
-//                            (TMA tiles through the exchange buffer) and run the epilogue.
+//                            saturate at 2^7 and are reported through the status word.  RoPE stays bf16.
+//   QK^T  (2 threads, CTA 0) S = Q K^T of a block is 20 x tcgen05.mma M=128 N=128 K=16 into one of two S buffers in
+//                            tensor memory; the two issuers take alternate blocks.  16 NoPE k-steps: A = Q from tensor
+//                            memory, B = the stage (K-major), f16 x f16 in decode (Q is converted once per item), bf16 x
+//                            bf16 in prefill.  N-half 0 comes from CTA 0's stage (feature half 0), N-half 1 from CTA 1's
+//                            (half 1); the A operand is lane-local, lanes 0-63 hold Q[:, half 0] and lanes 64-127
+//                            Q[:, half 1], so lanes 0-63 / 64-127 of the accumulator receive the two partial dot
+//                            products of the same 64 heads x 64 tokens.  The RoPE part of Q lives in shared memory
+//                            (tensor memory is full): its 2 k-steps are 4 products with the lanes of the other feature
+//                            half masked off (disable-output-lane).
+//   softmax (8, two teams)   team t (four warps, one per quarter of the tensor-memory lanes) takes the blocks of parity
+//                            t, so two blocks are in flight.  The two threads of a head in a team (the two feature
+//                            halves) add their partials through shared memory, apply the validity mask, run the online
+//                            softmax in base 2 and write P (f16 in decode, bf16 in prefill) as the A operand of PV.
+//                            The reference maximum moves lazily and is handed from team to team, block by block.  The
+//                            softmax warps also move each query's Q into tensor memory and run the epilogue.
 //   PV    (1 thread, CTA 0)  8 x tcgen05.mma M=128 N=256 K=16, A = P (shared memory, K-major), B = the same
 //                            stage viewed MN-major: CTA r's four NoPE panels are exactly V[:, 256r:256r+256].
 //                            O accumulates in tensor memory: lanes 0-63 = O[:, 0:256], lanes 64-127 = O[:, 256:512].
 //
-// Tensor memory (512 columns): O 0-255 | Q 256-399 | S 400-463.  All cross-role hand-offs are mbarriers; every
-// wait is bounded and a time-out raises an abort flag, sets *status and lets all roles fall through to the
-// teardown.  A shared-memory buffer that changes hands between generic-proxy accesses and TMA writes is fenced
-// with fence.proxy.async on the generic side before the barrier that hands it over.
+// Tensor memory (512 columns): O 0-255 | Q (NoPE) 256-383 | S buffers 384-447, 448-511.
+//
+// The stages form a ring used in a fixed order of positions.  The two positions before an item's first block carry the
+// item's Q, fetched by the stage-filling warps as far ahead as the KV rows (fill_q_positions); at the end of the item
+// before, the softmax warps copy it into tensor memory - the idle team while the last block's softmax still runs - and
+// the next item's first QK^T products overlap the last PV product and the epilogue.
+//
+// All cross-role hand-offs are mbarriers; every wait is bounded and a time-out raises an abort flag, sets *status and
+// lets all roles fall through to the teardown.  A shared-memory buffer that changes hands between generic-proxy
+// accesses and TMA writes is fenced with fence.proxy.async on the generic side before the barrier that hands it over.
 //
 // The kernel is persistent: a pair walks a list of work items - for decode the (request, block range)
 // pieces its tile-scheduler record assigns, for prefill every n-th query token - and the producers and
@@ -104,8 +114,7 @@ constexpr int IDX_LOOKAHEAD = 6;           // prefill: blocks the index prefetch
 // shared-memory map (offsets from a 1024-byte aligned base)
 enum Bar { KV_FULL = 0, KV_EMPTY = KV_FULL + MAX_STAGES, RAW_FULL = KV_EMPTY + MAX_STAGES /* [NGW][NRAW] */, RAW_EMPTY = RAW_FULL + NGW * NRAW /* [NGW][NRAW] */,
            S_FULL = RAW_EMPTY + NGW * NRAW /* [2 teams] */, S_EMPTY = S_FULL + 2 /* [2 teams] */, P_FULL = S_EMPTY + 2 /* [2 teams] */,
-           PV_DONE = P_FULL + 2 /* [2 teams] */, DEC = PV_DONE + 2 /* [2 teams] */, Q_FULL = DEC + 2, QT_FULL /* [2 feature halves] */,
-           QR_FULL = QT_FULL + 2, NUM_BARS };
+           PV_DONE = P_FULL + 2 /* [2 teams] */, DEC = PV_DONE + 2 /* [2 teams] */, Q_FULL = DEC + 2, QL_FULL /* [2 item parities] */, O_FREE = QL_FULL + 2, NUM_BARS };
 constexpr uint32_t SM_BAR = 0;
 constexpr uint32_t SM_TMEM = SM_BAR + NUM_BARS * 8;
 constexpr uint32_t SM_ABORT = SM_TMEM + 4;
@@ -136,6 +145,7 @@ struct Params {
   CUtensorMap map_scale;            // decode: byte view of the pool with a 16-byte box (the scale field of a row)
   CUtensorMap map_nope2, map_rope2, map_scale2;   // the same for the extra cache
   CUtensorMap map_q;               // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle)
+  CUtensorMap map_q_rope;          // the same view with boxes of 64 heads x 32 dims (64B swizzle)
   int q_tma;                     // the map above is valid; else Q is read with plain loads
   // decode with a second cache (extra_k_cache): its maps, geometry and index list; has_extra = 0 otherwise
   int has_extra, page2, rows_per_block2, extra_topk;
@@ -328,6 +338,53 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// 4-D tile load into this CTA's shared memory, completion on a local mbarrier.
+__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+
+// ---- Q travels through the stage ring -------------------------------------------------------------------
+// The stages are used in a fixed order of ring positions.  The two positions before the first block of a work item
+// hold that item's Q: position k = feature half k of this CTA's 64 heads, laid out exactly like a stage of KV rows (four
+// 128B-swizzled NoPE tiles of 64 dims and one 64B-swizzled RoPE tile of 32 dims, the heads in place of the tokens).  So
+// Q is fetched by the warps that fill the stages, as far ahead as the KV rows, and lies ready when the softmax warps
+// move it into tensor memory at the end of the item before.  Block n of the i-th item of a pair sits at ring position
+// (blocks of the items before) + n + 2 (i + 1).
+// Called by all lanes of a stage-filling warp (`pwarp` of NPW) at the start of an item: warps 0-3 fetch NoPE tile
+// `pwarp`, warp 4 the RoPE tile, of both positions; the bytes are counted on this CTA's QL_FULL barrier of the item's
+// parity (items alternate between two barriers: the ring may hold the Q of two short items at once, but never of three),
+// and every warp arrives on the leader's stage barrier so that its phase stays in step with the stage's uses.  `item`
+// is the item's number in the pair's list, (c2, c3) its outer coordinates in q.  Returns false when the kernel is aborting.
+template <class P>
+__device__ __forceinline__ bool fill_q_positions(const P& p, const Ctx& c, uint32_t rank, int pwarp, int lane, int item, int c2, int c3, uint32_t& pos) {
+  const int nst = p.mode == 0 ? NSTAGE_DECODE : NSTAGE_PREFILL;
+  const int head0 = blockIdx.z * 128 + (int)rank * 64;
+#pragma unroll 1
+  for (int k = 0; k < 2; ++k, ++pos) {
+    const int st = pos % nst;
+    const uint32_t use = pos / nst;
+    const bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 16);
+    if (!__all_sync(0xffffffffu, ok)) return false;
+    if (lane == 0) {
+      if (pwarp < 5) {
+        const uint32_t bar = bar_addr(c, QL_FULL + (item & 1)), dst = c.base + SM_STAGE + (uint32_t)st * STAGE_BYTES;
+        if (!p.q_tma) mbar_arrive(bar);                 // Q is read with plain loads: nothing to fetch
+        else if (pwarp < 4) {
+          mbar_expect_tx(bar, PANEL);
+          tma_tile_4d(dst + pwarp * PANEL, &p.map_q, 256 * k + 64 * pwarp, head0, c2, c3, bar);
+        } else {
+          mbar_expect_tx(bar, T * 64);
+          tma_tile_4d(dst + ROPE_PANEL, &p.map_q_rope, 512 + 32 * k, head0, c2, c3, bar);
+        }
+      }
+      arrive_leader(c, KV_FULL + st);
+    }
+  }
+  return true;
+}
+
 // ---- FP8 dequantisation (decode) --------------------------------------------------------------------------
 // Decode stages the NoPE half in fp16, not bf16: e4m3 -> f16 is one exact conversion per pair and the scale
 // is one packed multiply, four times fewer instructions than going through fp32 to bf16.  fp8 * 2^k is exact
@@ -396,12 +453,14 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
   for (int k = 0; k < IDX_LOOKAHEAD; ++k) feed_block(k);
   const int q = lane / 5, kind = lane - 5 * q;
   static_assert(PROWS == 8, "two four-row groups per producer warp");
-  for (uint32_t g = 0; gat.live; ++g, gat.advance(p, rec)) {
+  uint32_t pos = 0;                                   // ring position
+  for (uint32_t g = 0; gat.live; ++g, ++pos, gat.advance(p, rec)) {
+    if (gat.n == 0 && !fill_q_positions(p, c, rank, pwarp, lane, gat.item, gat.it.req, 0, pos)) return;
     // groups 0 .. g+IDX_LOOKAHEAD-1 are committed; with at most IDX_LOOKAHEAD-1 pending, group g has landed
     cp_async_wait<IDX_LOOKAHEAD - 1>();
     __syncwarp();
-    const int st = g % nst;
-    const uint32_t use = g / nst;
+    const int st = pos % nst;
+    const uint32_t use = pos / nst;
     bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 12);
     if (!__all_sync(0xffffffffu, ok)) return;
     const uint32_t dst = stage_addr(c, st);
@@ -530,8 +589,17 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     for (int i = 0; get_item(p, rec, i, it); ++i) total_blocks += (uint32_t)num_blocks(it);
   }
   bool clipped = false;      // a scale beyond what the fp16 stage can hold was met (the values were clipped)
-  for (uint32_t g = 0; g < total_blocks; ++g) {
-    const int st = g % NSTAGE_DECODE, slot = g % NRAW;
+  uint32_t pos = 0;          // ring position
+  int item = 0, n = 0, nb = 0;
+  for (uint32_t g = 0; g < total_blocks; ++g, ++pos) {
+    if (n == 0) {            // first block of an item: its Q goes into the two ring positions before
+      Item it;
+      get_item(p, rec, item, it);
+      nb = num_blocks(it);
+      if (!fill_q_positions(p, c, rank, pwarp, lane, item, it.sq, it.req, pos)) return;
+    }
+    if (++n >= nb) { n = 0; ++item; }
+    const int st = pos % NSTAGE_DECODE, slot = g % NRAW;
     bool ok = wait(c, RAW_FULL + gw * NRAW + slot, g / NRAW, 14);
     if (!__all_sync(0xffffffffu, ok)) return;
     const uint32_t raw = c.base + SM_RAW + (uint32_t)slot * RAW_BYTES, stage = stage_addr(c, st);
@@ -557,7 +625,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       dequant_chunk_f16(in[it], scale_to_half2(scale), lo[it], hi[it]);
     }
     // only the stores need the stage: everything above overlaps the products that still read its previous contents
-    const uint32_t use = g / NSTAGE_DECODE;
+    const uint32_t use = pos / NSTAGE_DECODE;
     ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
     if (!__all_sync(0xffffffffu, ok)) return;
 #pragma unroll
@@ -602,8 +670,9 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
     if (!wait(c, Q_FULL, i, 21)) return;
     const uint32_t seq_end = seq + (uint32_t)num_blocks(it);
     for (seq += (seq ^ k) & 1u; seq < seq_end; seq += 2) {
-      const int s = seq % nst;
-      if (!wait(c, KV_FULL + s, seq / nst, 22)) return;
+      const uint32_t pos = seq + 2u * (uint32_t)(i + 1);       // ring position: two per item hold its Q
+      const int s = pos % nst;
+      if (!wait(c, KV_FULL + s, pos / nst, 22)) return;
       if (seq >= 2 && !wait(c, S_EMPTY + k, (seq >> 1) - 1, 23)) return;
       tc_fence_after_sync();
       const uint64_t b0 = smem_desc_kmajor(stage_addr(c, s));
@@ -630,10 +699,13 @@ __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint3
   uint32_t seq = 0;
   for (int i = 0; get_item(p, rec, i, it); ++i) {
     const int nb = num_blocks(it);
+    // the item's first product overwrites O: the epilogue of the item before has read it
+    if (i > 0 && !wait(c, O_FREE, i - 1, 33)) return;
     for (int n = 0; n < nb; ++n, ++seq) {
-      const int s = seq % nst, b = seq & 1;
+      const uint32_t pos = seq + 2u * (uint32_t)(i + 1);
+      const int s = pos % nst, b = seq & 1;
       if (!wait(c, P_FULL + b, seq >> 1, 31)) return;
-      if (!wait(c, KV_FULL + s, seq / nst, 32)) return;
+      if (!wait(c, KV_FULL + s, pos / nst, 32)) return;
       tc_fence_after_sync();
       const uint64_t a0 = smem_desc_kmajor(c.base + SM_P + b * P_BYTES);
       const uint64_t v0 = smem_desc_mnmajor(stage_addr(c, s), PANEL);
@@ -662,16 +734,15 @@ __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint3
 __device__ __forceinline__ void pair_sync(int warp) { asm volatile("bar.sync %0, 64;" ::"r"(3 + 2 * (warp >> 2) + (warp & 1)) : "memory"); }
 __device__ __forceinline__ void quad_sync(int warp) { asm volatile("bar.sync %0, 128;" ::"r"(1 + (warp & 1)) : "memory"); }
 __device__ __noinline__ void leave_group(uint32_t leave_word, int warp) {
-  // Named barriers have no time-out, so a leaving warp keeps feeding the four barriers it takes part in (its pair,
-  // its quad, its feature half and the all-warps barrier of the Q load) until every softmax warp of the CTA has
-  // left or a bound is reached: whoever still waits in one of them is released, meets the abort flag at its next
-  // mbarrier wait and ends up here too.
+  // Named barriers have no time-out, so a leaving warp keeps feeding the three barriers it takes part in (its pair,
+  // its quad and the all-warps barrier of the Q hand-over) until every softmax warp of the CTA has left or a bound is
+  // reached: whoever still waits in one of them is released, meets the abort flag at its next mbarrier wait and ends
+  // up here too.
   __syncwarp();
   if ((threadIdx.x & 31) == 0) asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(leave_word) : "memory");
   for (int it = 0; it < (1 << 16); ++it) {
     asm volatile("bar.arrive %0, 64;" ::"r"(3 + 2 * (warp >> 2) + (warp & 1)) : "memory");
     asm volatile("bar.arrive %0, 128;" ::"r"(1 + (warp & 1)) : "memory");
-    asm volatile("bar.arrive %0, 128;" ::"r"(7 + ((warp >> 1) & 1)) : "memory");
     asm volatile("bar.arrive 9, 256;" ::: "memory");
     uint32_t left;
     asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(left) : "r"(leave_word));
@@ -744,74 +815,33 @@ __device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const I
   fence_async_smem();      // the panel is read by the MMAs (async proxy)
   tmem_st_wait();
 }
-// 4-D tile load into this CTA's shared memory, completion on a local mbarrier.
-__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
-}
-// The 128 softmax threads of one feature half (four warps) meet here while they load Q.
-__device__ __forceinline__ void half_sync(int half) { asm volatile("bar.sync %0, 128;" ::"r"(7 + half) : "memory"); }
-
-// Q of one query through TMA.  RoPE: the 64 heads x 64 dims go straight into the RoPE panel, where the MMAs read them.
-// NoPE: the 64 heads x 256 dims of a feature half arrive as four tiles of 64 dims in that half's 8 KB of the exchange
-// buffer, which is idle between two work items; each thread copies its 32 dims of the tile to its tensor-memory lane,
-// and the next tile is requested as soon as all 128 threads of the half have read the current one.
-// `uses` counts the NoPE tiles this thread has waited for and `items` the RoPE tiles (barrier parities).  Returns false
-// when aborting.  `pre()` runs while the first tiles are in flight (false = aborting) and `post(r)` after NoPE tile r
-// has been copied: the caller uses them to run the previous item's epilogue in the shadow of the tiles' latency.
-template <class P, class Pre, class Post>
-__device__ __forceinline__ bool load_q_tma(const P& p, const Ctx& c, const Item& it, uint32_t tmem_lane, int head0, int h, int half,
-                                           int g, bool issuer, uint32_t& uses, uint32_t& items, uint32_t& qmax, int stage_p, int pv_wait,
-                                           Pre pre, Post post) {
-  // tiles of feature half 0 land in the exchange buffer, those of half 1 in P buffer `stage_p`: the one that the query's
-  // last PV product does not read.  Its own last reader is PV product number `pv_wait` (-1: none), long issued by now.
-  const uint32_t buf = half == 0 ? c.base + SM_XCHG : c.base + SM_P + (uint32_t)stage_p * P_BYTES;
-  const uint32_t bar = bar_addr(c, QT_FULL + half), bar_rope = bar_addr(c, QR_FULL);
-  const int c2 = p.mode == 0 ? it.sq : it.req, c3 = p.mode == 0 ? it.req : 0;
-  auto request = [&](int r) {
-    mbar_expect_tx(bar, 64 * 128);
-    tma_tile_4d(buf, &p.map_q, 256 * half + 64 * r, head0, c2, c3, bar);
-  };
-  // Every softmax warp has consumed the query's last S, so its QK^T products are complete and Q may be replaced; and
-  // every warp has finished with the exchange buffer (last block's partial sums) before a tile overwrites it: each
-  // thread orders its own generic-proxy accesses to the buffer before the TMA writes that follow the barrier.
-  fence_async_smem();
-  asm volatile("bar.sync 9, 256;" ::: "memory");
-  if (issuer) {
-    if (half == 0) {
-      mbar_expect_tx(bar_rope, QROPE_BYTES);
-      tma_tile_4d(c.base + SM_QROPE, &p.map_q, 512, head0, c2, c3, bar_rope);
-    } else if (pv_wait >= 0) {
-      wait(c, PV_DONE + stage_p, (uint32_t)pv_wait >> 1, 46);      // on a time-out the tile waits below end the role
-    }
-    request(0);
-  }
-  if (!pre()) return false;
-#pragma unroll 1
+// Q of one query from its two ring positions (see fill_q_positions) into tensor memory (NoPE) and into the RoPE panel.
+// `src` is the stage that holds this thread's feature half.  The thread copies, of each of the four NoPE tiles, the 32
+// dims of its column group to its tensor-memory lane, and the 16 RoPE dims 32 half + 16 g of its head.
+template <class P>
+__device__ __forceinline__ void copy_q_from_stage(const P& p, const Ctx& c, uint32_t src, uint32_t tmem_lane, int h, int half, int g, uint32_t& qmax) {
+#pragma unroll
   for (int r = 0; r < 4; ++r) {
-    if (!mbar_wait_abortable(bar, uses & 1u, c.abort_flag)) { if (*c.abort_flag == 0) raise_abort(c, 48); return false; }
-    ++uses;
     uint32_t v[16];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const uint4 t = lds_16(buf + swz(h, 4 * g + k));
+      const uint4 t = lds_16(src + r * PANEL + swz(h, 4 * g + k));
       v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
     }
-    fence_async_smem();      // my reads of this tile before the next tile's TMA writes (or the block loop's stores)
-    half_sync(half);
-    if (issuer && r < 3) request(r + 1);
     if (p.mode == 0) {   // decode multiplies the NoPE part in fp16
 #pragma unroll
       for (int k = 0; k < 16; ++k) { qmax = absmax_bf16x2(qmax, v[k]); v[k] = bf16x2_to_f16x2(v[k]); }
     }
     tmem_st16(tmem_lane + TM_Q + 32 * r + 16 * g, v);
-    post(r);
   }
-  if (!mbar_wait_abortable(bar_rope, items & 1u, c.abort_flag)) { if (*c.abort_flag == 0) raise_abort(c, 49); return false; }
-  ++items;
+  const uint32_t rp = src + ROPE_PANEL + (uint32_t)h * 64u, sw = ((uint32_t)h >> 1) & 3u;
+  const uint4 e0 = lds_16(rp + (((uint32_t)(2 * g) ^ sw) << 4)), e1 = lds_16(rp + (((uint32_t)(2 * g + 1) ^ sw) << 4));
+  st_shared16(c.base + SM_QROPE + swz(h, 4 * half + 2 * g), e0);
+  st_shared16(c.base + SM_QROPE + swz(h, 4 * half + 2 * g + 1), e1);
+  // the panel is read by the MMAs (async proxy), and this thread's reads of the stages come before the TMA writes of
+  // their next use
+  fence_async_smem();
   tmem_st_wait();
-  return true;
 }
 
 // Asks L2 for the part of a query's Q row that load_q_to_tmem will read.
@@ -856,24 +886,36 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
 
   Item it, it_next;
   bool have = get_item(p, rec, 0, it);
-  const int head0 = blockIdx.z * 128 + (int)rank * 64;
-  const bool q_issuer = h == 0 && g == 0;
-  uint32_t qt_uses = 0, qr_items = 0;
+  const int nst = num_stages(p);
   uint32_t q_absmax = 0;                     // decode: largest |q| of the NoPE part seen by this thread (Q is staged in fp16)
-  if (have) {
-    if (p.q_tma) {
-      if (!load_q_tma(p, c, it, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, 1, -1, [] { return true; }, [](int) {})) { leave_group(leave_word, warp); return; }
-    } else {
-      load_q_to_tmem(p, c, it, tmem_lane, head, h, half, g, q_absmax);
-    }
+  // Q of the pair's `index`-th item, which lies in ring positions pos and pos + 1, goes to tensor memory and to the
+  // RoPE panel; the caller has made sure that no QK^T product that reads the Q before is still running.  Then the two
+  // stages are handed back: the team that comes `early` only reports at the barrier of all softmax warps, the other
+  // one waits there and its first thread releases the stages.  Returns false when aborting.
+  auto take_q = [&](const Item& q_it, int index, uint32_t pos, bool early) -> bool {
+    const bool ok = wait(c, QL_FULL + (index & 1), index >> 1, 48);
+    if (!__all_sync(0xffffffffu, ok)) return false;
+    if (p.q_tma) copy_q_from_stage(p, c, stage_addr(c, (int)((pos + (uint32_t)half) % (uint32_t)nst)), tmem_lane, h, half, g, q_absmax);
+    else load_q_to_tmem(p, c, q_it, tmem_lane, head, h, half, g, q_absmax);
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) arrive_leader(c, Q_FULL);
-  }
+    if (early) {
+      asm volatile("bar.arrive 9, 256;" ::: "memory");
+    } else {
+      asm volatile("bar.sync 9, 256;" ::: "memory");
+      if (L == 0) {
+        mbar_arrive(bar_addr(c, KV_EMPTY + (int)(pos % (uint32_t)nst)));
+        mbar_arrive(bar_addr(c, KV_EMPTY + (int)((pos + 1u) % (uint32_t)nst)));
+      }
+    }
+    return true;
+  };
+  if (have && !take_q(it, 0, 0u, team == 0)) { leave_group(leave_word, warp); return; }
   uint32_t seq0 = 0;                         // number of blocks of the items before this one
   for (int i = 0; have; ++i) {
     const bool have_next = get_item(p, rec, i + 1, it_next);
-    if (have_next) prefetch_q(p, it_next, head, half, g);
+    if (have_next && !p.q_tma) prefetch_q(p, it_next, head, half, g);
     // m_mine: the reference maximum that l_sum is relative to; m_true: largest logit (base 2) of this team's blocks
     float m_mine = -CUDART_INF_F, m_true = -CUDART_INF_F, l_sum = 0.f;
     const uint32_t seq_end = seq0 + (uint32_t)num_blocks(it);
@@ -986,13 +1028,15 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     bool empty = true;
     float* dst_f32 = nullptr;
     __nv_bfloat16* dst_bf16 = nullptr;
-    // Runs after a barrier of all softmax warps: every S of this query has been consumed, so all its QK^T products
-    // are complete, and both teams have stored their last reference maximum.
+    const bool mine_last = (last & 1u) == (uint32_t)team;     // this team took the query's last block
     auto epi_begin = [&]() -> bool {            // row sums and maxima of the quad, output scale, destination
+      // the query's final reference maximum is the one the last block's team has settled
+      bool ok = mine_last || wait(c, DEC + (team ^ 1), last >> 1, 43);
+      if (!__all_sync(0xffffffffu, ok)) return false;
       m_fin = lds_f32(c.base + SM_MREF + 4u * (64 * (last & 1u) + h));
       sts_f32(sum_base + 256u * slot, m_mine == m_fin ? l_sum : l_sum * exp2f(m_mine - m_fin));
       if (half == 0) sts_f32(mtrue_base + 256u * team, m_true);   // the two halves of a team hold the same value
-      bool ok = wait(c, PV_DONE + (last & 1), last >> 1, 47);
+      ok = wait(c, PV_DONE + (last & 1), last >> 1, 47);
       if (!__all_sync(0xffffffffu, ok)) return false;
       tc_fence_after_sync();
       quad_sync(warp);
@@ -1041,27 +1085,25 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         p.max_logits[it.row * p.h_q + head] = empty ? -CUDART_INF_F : m_true * LN2;
       }
     };
-    // With the TMA path the epilogue's four chunks run between the Q tiles, in the shadow of their latency;
-    // either way the next item's first QK^T overlaps the rest of the epilogue.
-    if (have_next && p.q_tma) {
-      if (!load_q_tma(p, c, it_next, tmem_lane, head0, h, half, g, q_issuer, qt_uses, qr_items, q_absmax, (int)((last ^ 1u) & 1u), (int)last - 1, epi_begin, epi_chunk)) { leave_group(leave_word, warp); return; }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) arrive_leader(c, Q_FULL);
-    } else {
-      asm volatile("bar.sync 9, 256;" ::: "memory");
-      if (have_next) {
-        load_q_to_tmem(p, c, it_next, tmem_lane, head, h, half, g, q_absmax);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) arrive_leader(c, Q_FULL);
-      }
-      if (!epi_begin()) { leave_group(leave_word, warp); return; }
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) epi_chunk(ch);
+    // The next query's Q first: it waits in its ring positions, and once it is in tensor memory the next query's first
+    // QK^T products run beside this query's last PV product and the epilogue.  Q may be replaced when every QK^T
+    // product of this query is complete: the team that took the last block knows (it has read that S, and the block
+    // before was settled before it started); the other team, idle since the block before, waits for the last S without
+    // consuming it and moves its share of Q while the last block's softmax runs.
+    if (have_next) {
+      const bool ok = mine_last || wait(c, S_FULL + (team ^ 1), last >> 1, 46);
+      if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
+      tc_fence_after_sync();
+      if (!take_q(it_next, i + 1, seq_end + 2u * (uint32_t)(i + 1), !mine_last)) { leave_group(leave_word, warp); return; }
     }
+    if (!epi_begin()) { leave_group(leave_word, warp); return; }
+#pragma unroll 1
+    for (int ch = 0; ch < 4; ++ch) epi_chunk(ch);
     epi_end();
+    // O has been read: the next query's first PV product may overwrite it
     tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) arrive_leader(c, O_FREE);
     it = it_next;
     have = have_next;
   }
@@ -1107,9 +1149,9 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
       mbar_init(bar_addr(c, PV_DONE + b), 1);
       mbar_init(bar_addr(c, DEC + b), NSW / 2);              // the warps of one team of this CTA
     }
-    mbar_init(bar_addr(c, QR_FULL), 1);
     mbar_init(bar_addr(c, Q_FULL), 2 * NSW);
-    for (int hf = 0; hf < 2; ++hf) mbar_init(bar_addr(c, QT_FULL + hf), 1);
+    mbar_init(bar_addr(c, O_FREE), 2 * NSW);
+    for (int b = 0; b < 2; ++b) mbar_init(bar_addr(c, QL_FULL + b), 2 * 5);   // five fetching warps per ring position (fill_q_positions)
     mbar_init_fence();
   }
   if (warp == QK_WARP) { tmem_alloc<2>(c.base + SM_TMEM, TM_COLS); tmem_relinquish<2>(); }
@@ -1237,7 +1279,8 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.sm_scale * LOG2E;
   p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
   p.q_stride0 = a.q_stride_b; p.q_stride1 = a.q_stride_s; p.q_stride_h = a.q_stride_h;
-  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B) &&
+            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 32, CU_TENSOR_MAP_SWIZZLE_64B);
   p.indices = a.indices; p.idx_stride0 = a.idx_stride_b; p.idx_stride1 = a.idx_stride_s;
   p.topk_length = a.topk_length; p.attn_sink = a.attn_sink;
   p.kv_rows = reinterpret_cast<const uint8_t*>(a.kv);
@@ -1292,7 +1335,8 @@ int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream) {
   // features of a row are V either way, and zero features add nothing to q . k.
   const int d_qk = a.d_qk == 0 ? D_QK : a.d_qk;
   p.d_qk = d_qk;
-  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 64, CU_TENSOR_MAP_SWIZZLE_128B, d_qk);
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 64, CU_TENSOR_MAP_SWIZZLE_128B, d_qk) &&
+            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, 1, a.q_stride_h, a.q_stride_s, a.q_stride_s * a.s_q, 32, CU_TENSOR_MAP_SWIZZLE_64B, d_qk);
   p.indices = a.indices; p.idx_stride0 = a.idx_stride_s; p.idx_stride1 = 0;
   p.topk_length = a.topk_length; p.attn_sink = a.attn_sink;
   p.kv_bf16 = reinterpret_cast<const __nv_bfloat16*>(a.kv);
