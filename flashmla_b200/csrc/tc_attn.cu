@@ -147,6 +147,9 @@ struct Params {
   CUtensorMap map_q;               // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle)
   CUtensorMap map_q_rope;          // the same view with boxes of 64 heads x 32 dims (64B swizzle)
   int q_tma;                     // the map above is valid; else Q is read with plain loads
+  CUtensorMap map_out;             // out as (512, h_q, s_q, b) / (512, h_q, queries, 1) bf16: boxes of 32 heads x 32 dims (64B swizzle)
+  CUtensorMap map_acc;             // decode: o_accum as (512, h_q, rows / h_q, 1) fp32: boxes of 32 heads x 16 dims (64B swizzle)
+  int out_tma;                   // the two maps above are valid; else the epilogue stores with plain stores
   // decode with a second cache (extra_k_cache): its maps, geometry and index list; has_extra = 0 otherwise
   int has_extra, page2, rows_per_block2, extra_topk;
   int64_t total_rows2;
@@ -344,6 +347,16 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
 }
+
+// 4-D tile store from this CTA's shared memory (bulk async group of the issuing thread).  No coordinate is negative.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's bulk stores have read their shared-memory source / have completed
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- Q travels through the stage ring -------------------------------------------------------------------
 // The stages are used in a fixed order of ring positions.  The two positions before the first block of a work item
@@ -1052,12 +1065,57 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       else dst_bf16 = p.out + (it.row * p.h_q + head) * D_V + col0;
       return true;
     };
+    // A plain store of a warp would touch 32 rows of the output with 16 bytes each, one memory transaction per lane, and
+    // the epilogue would cost as much as several blocks.  So the warp stages its 32 heads x 32 columns (x 16 for fp32
+    // partial results) in its quarter of the team's P buffer, idle between two queries, in the 64B-swizzled layout of a
+    // TMA box, and one lane sends the box off; the buffer is rewritten once the previous box has been read.  The quarter
+    // lies in the 4 KB that the warp shares with the other warp of its pair in the block loop (see xoff), and the pair
+    // meets after its last boxes have been read, before either goes back to the block loop.
+    const uint32_t scratch = pbuf + 4096u * (uint32_t)(warp & 1) + 2048u * (uint32_t)((warp >> 1) & 1), scratch_row = scratch + (uint32_t)lane * 64u;
+    const uint32_t scratch_sw = ((uint32_t)lane >> 1) & 3u;
+    const int head_warp = head - lane;          // first head of this warp
     auto epi_chunk = [&](int ch) {              // 32 columns of O: scale, convert, store
       if (!real_head) return;                   // warp-uniform: a warp's 32 heads lie in one 64-head half
       uint32_t o[32];
       tmem_ld32(tmem_lane + TM_O + 128 * g + 32 * ch, o);
       tmem_ld_wait();
-      if (it.split) {
+      if (p.out_tma) {
+        const int col = 256 * half + 128 * g + 32 * ch;
+        if (it.split) {
+          const int acc_row = (int)(it.row / p.h_q);
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            if (lane == 0) bulk_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              st_shared16(scratch_row + (((uint32_t)k ^ scratch_sw) << 4),
+                          make_uint4(__float_as_uint(__uint_as_float(o[16 * sub + 4 * k]) * mul), __float_as_uint(__uint_as_float(o[16 * sub + 4 * k + 1]) * mul),
+                                     __float_as_uint(__uint_as_float(o[16 * sub + 4 * k + 2]) * mul), __float_as_uint(__uint_as_float(o[16 * sub + 4 * k + 3]) * mul)));
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) { tma_store_4d(&p.map_acc, col + 16 * sub, head_warp, acc_row, 0, scratch); bulk_commit(); }
+          }
+        } else {
+          if (lane == 0) bulk_wait_read();
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * mul, __uint_as_float(o[8 * k + 1]) * mul);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * mul, __uint_as_float(o[8 * k + 3]) * mul);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * mul, __uint_as_float(o[8 * k + 5]) * mul);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * mul, __uint_as_float(o[8 * k + 7]) * mul);
+            st_shared16(scratch_row + (((uint32_t)k ^ scratch_sw) << 4), v);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&p.map_out, col, head_warp, p.mode == 0 ? it.sq : (int)it.row, p.mode == 0 ? it.req : 0, scratch);
+            bulk_commit();
+          }
+        }
+      } else if (it.split) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<float4*>(dst_f32 + 32 * ch + 4 * j) =
@@ -1103,10 +1161,16 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     // O has been read: the next query's first PV product may overwrite it
     tc_fence_before_sync();
     __syncwarp();
-    if (lane == 0) arrive_leader(c, O_FREE);
+    if (lane == 0) {
+      arrive_leader(c, O_FREE);
+      if (p.out_tma) bulk_wait_read();          // the P buffer goes back to the block loop
+    }
+    __syncwarp();
+    if (p.out_tma) pair_sync(warp);
     it = it_next;
     have = have_next;
   }
+  if (p.out_tma && lane == 0) bulk_wait_all();   // this thread's output boxes are written before the CTA goes
   if (p.mode == 0 && __any_sync(0xffffffffu, beyond_f16(q_absmax)) && lane == 0 && c.status) atomicCAS(c.status, 0, FMLA_STATUS_CLIPPED);
 }
 
@@ -1197,6 +1261,16 @@ static bool make_q_map(CUtensorMap* map, const void* q, int h_q, uint64_t n1, ui
   const uint64_t strides[3] = {(uint64_t)stride_h * 2, (uint64_t)stride1 * 2, (uint64_t)stride2 * 2};
   const uint32_t box[4] = {box_cols, 64, 1, 1};
   return tmap::encode(map, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, swizzle) == 0;
+}
+// An output tensor viewed as (512, h_q, n1, n2) with element strides; box = box_cols dims x 32 heads, 64 bytes wide,
+// 64B swizzle.  Returns false if the driver refuses the strides (the epilogue then stores with plain stores).
+static bool make_out_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, int h_q, uint64_t n1, uint64_t n2,
+                         int64_t stride_h, int64_t stride1, int64_t stride2, uint32_t box_cols) {
+  if (stride_h <= 0 || stride1 <= 0 || stride2 <= 0 || n1 == 0 || n2 == 0) return false;
+  const uint64_t dims[4] = {(uint64_t)D_V, (uint64_t)h_q, n1, n2};
+  const uint64_t strides[3] = {(uint64_t)stride_h * elem_bytes, (uint64_t)stride1 * elem_bytes, (uint64_t)stride2 * elem_bytes};
+  const uint32_t box[4] = {box_cols, 32, 1, 1};
+  return tmap::encode(map, base, dt, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B) == 0;
 }
 // 2-D map over `rows` rows of `cols` elements with a row pitch of `pitch_bytes`; one box is `box_cols` elements of one row.
 static int make_row_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, uint64_t cols, uint64_t rows,
@@ -1293,6 +1367,11 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   p.lse = a.lse; p.lse_stride0 = a.lse_stride_b; p.lse_stride1 = a.lse_stride_s;
   p.o_accum = a.o_accum; p.lse_accum = a.lse_accum;
   p.status = a.status;
+  {   // o_accum holds (b + num_sm_parts) * s_q rows of h_q x 512
+    const uint64_t acc_rows = (uint64_t)(a.b + a.num_sm_parts) * (uint64_t)a.s_q;
+    p.out_tma = tc::make_out_map(&p.map_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.o_stride_h, a.o_stride_s, a.o_stride_b, 32) &&
+                tc::make_out_map(&p.map_acc, a.o_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.h_q, acc_rows, 1, D_V, (int64_t)a.h_q * D_V, (int64_t)(acc_rows * a.h_q) * D_V, 16);
+  }
   // Rows are addressed as base + row * 656 with a 32-bit row number, so a block stride must be a whole number of rows
   // (the reference has the same requirement, csrc/sm100/decode/head64/kernel.cuh:911-912); tc_decode_supported() tells
   // the caller, which then takes the CUDA-core kernel.
@@ -1344,6 +1423,7 @@ int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream) {
   p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
   p.lse = a.lse; p.max_logits = a.max_logits;
   p.status = a.status;
+  p.out_tma = tc::make_out_map(&p.map_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.h_q, (uint64_t)a.s_q, 1, D_V, (int64_t)a.h_q * D_V, (int64_t)a.h_q * D_V * a.s_q, 32);
   if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_qk, (uint64_t)a.s_kv, (uint64_t)a.kv_stride_s * 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d_qk, (uint64_t)a.s_kv, (uint64_t)a.kv_stride_s * 2, 32, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
   const int groups = (a.h_q + 127) / 128;
