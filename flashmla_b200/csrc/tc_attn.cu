@@ -1074,15 +1074,23 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     const uint32_t scratch = pbuf + 4096u * (uint32_t)(warp & 1) + 2048u * (uint32_t)((warp >> 1) & 1), scratch_row = scratch + (uint32_t)lane * 64u;
     const uint32_t scratch_sw = ((uint32_t)lane >> 1) & 3u;
     const int head_warp = head - lane;          // first head of this warp
-    auto epi_chunk = [&](int ch) {              // 32 columns of O: scale, convert, store
+    // The four chunks of 32 columns through the staging buffer: the next chunk's tensor-memory load is issued before
+    // the current chunk waits for the buffer, so that the two latencies overlap.
+    auto epi_chunks_tma = [&]() {
       if (!real_head) return;                   // warp-uniform: a warp's 32 heads lie in one 64-head half
-      uint32_t o[32];
-      tmem_ld32(tmem_lane + TM_O + 128 * g + 32 * ch, o);
-      tmem_ld_wait();
-      if (p.out_tma) {
-        const int col = 256 * half + 128 * g + 32 * ch;
+      uint32_t o[2][32];
+      const uint32_t src = tmem_lane + TM_O + 128 * g;
+      const int col0 = 256 * half + 128 * g;
+      const int acc_row = it.split ? (int)(it.row / p.h_q) : 0;
+      tmem_ld32(src, o[0]);
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t (&cur)[32] = o[ch & 1];
+        tmem_ld_wait();
+        if (ch < 3) tmem_ld32(src + 32 * (ch + 1), o[(ch + 1) & 1]);
         if (it.split) {
-          const int acc_row = (int)(it.row / p.h_q);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cur[j] = __float_as_uint(__uint_as_float(cur[j]) * mul);
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub) {
             if (lane == 0) bulk_wait_read();
@@ -1090,32 +1098,39 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               st_shared16(scratch_row + (((uint32_t)k ^ scratch_sw) << 4),
-                          make_uint4(__float_as_uint(__uint_as_float(o[16 * sub + 4 * k]) * mul), __float_as_uint(__uint_as_float(o[16 * sub + 4 * k + 1]) * mul),
-                                     __float_as_uint(__uint_as_float(o[16 * sub + 4 * k + 2]) * mul), __float_as_uint(__uint_as_float(o[16 * sub + 4 * k + 3]) * mul)));
+                          make_uint4(cur[16 * sub + 4 * k], cur[16 * sub + 4 * k + 1], cur[16 * sub + 4 * k + 2], cur[16 * sub + 4 * k + 3]));
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) { tma_store_4d(&p.map_acc, col + 16 * sub, head_warp, acc_row, 0, scratch); bulk_commit(); }
+            if (lane == 0) { tma_store_4d(&p.map_acc, col0 + 32 * ch + 16 * sub, head_warp, acc_row, 0, scratch); bulk_commit(); }
           }
         } else {
+          uint4 v[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            v[k].x = pack_bf16x2(__uint_as_float(cur[8 * k]) * mul, __uint_as_float(cur[8 * k + 1]) * mul);
+            v[k].y = pack_bf16x2(__uint_as_float(cur[8 * k + 2]) * mul, __uint_as_float(cur[8 * k + 3]) * mul);
+            v[k].z = pack_bf16x2(__uint_as_float(cur[8 * k + 4]) * mul, __uint_as_float(cur[8 * k + 5]) * mul);
+            v[k].w = pack_bf16x2(__uint_as_float(cur[8 * k + 6]) * mul, __uint_as_float(cur[8 * k + 7]) * mul);
+          }
           if (lane == 0) bulk_wait_read();
           __syncwarp();
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * mul, __uint_as_float(o[8 * k + 1]) * mul);
-            v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * mul, __uint_as_float(o[8 * k + 3]) * mul);
-            v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * mul, __uint_as_float(o[8 * k + 5]) * mul);
-            v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * mul, __uint_as_float(o[8 * k + 7]) * mul);
-            st_shared16(scratch_row + (((uint32_t)k ^ scratch_sw) << 4), v);
-          }
+          for (int k = 0; k < 4; ++k) st_shared16(scratch_row + (((uint32_t)k ^ scratch_sw) << 4), v[k]);
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_4d(&p.map_out, col, head_warp, p.mode == 0 ? it.sq : (int)it.row, p.mode == 0 ? it.req : 0, scratch);
+            tma_store_4d(&p.map_out, col0 + 32 * ch, head_warp, p.mode == 0 ? it.sq : (int)it.row, p.mode == 0 ? it.req : 0, scratch);
             bulk_commit();
           }
         }
-      } else if (it.split) {
+      }
+    };
+    auto epi_chunk = [&](int ch) {              // 32 columns of O with plain stores: scale, convert, store
+      if (!real_head) return;
+      uint32_t o[32];
+      tmem_ld32(tmem_lane + TM_O + 128 * g + 32 * ch, o);
+      tmem_ld_wait();
+      if (it.split) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<float4*>(dst_f32 + 32 * ch + 4 * j) =
@@ -1155,8 +1170,11 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       if (!take_q(it_next, i + 1, seq_end + 2u * (uint32_t)(i + 1), !mine_last)) { leave_group(leave_word, warp); return; }
     }
     if (!epi_begin()) { leave_group(leave_word, warp); return; }
+    if (p.out_tma) epi_chunks_tma();
+    else {
 #pragma unroll 1
-    for (int ch = 0; ch < 4; ++ch) epi_chunk(ch);
+      for (int ch = 0; ch < 4; ++ch) epi_chunk(ch);
+    }
     epi_end();
     // O has been read: the next query's first PV product may overwrite it
     tc_fence_before_sync();
