@@ -265,6 +265,39 @@ __device__ __forceinline__ void umma_commit(uint32_t bar, uint16_t cta_mask) {
                  ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
+// ---- MMA issue by a whole warp --------------------------------------------------------------------------------
+// The variants below are executed by all 32 lanes of a warp with identical operands; elect.sync picks the one lane that
+// issues.  Because the warp stays converged and the operands are the same in every lane, the compiler keeps them in
+// uniform registers, which is where the instruction takes them from; issued from inside a one-lane branch each product
+// pays for moving them there, three times the cost (measured on B200: 20 products + commit in 350 instead of 1040 cycles).
+// All products and the commit that covers them must come from these variants (the same lane is elected every time).
+__device__ __forceinline__ void umma_ts_pair_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+               "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+               "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// see umma_ss_pair_masked for lanes_off
+__device__ __forceinline__ void umma_ss_pair_masked_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate,
+                                                          const uint32_t (&lanes_off)[8]) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+               "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5,%6,%7,%8,%9,%10,%11,%12}, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(lanes_off[0]), "r"(lanes_off[1]), "r"(lanes_off[2]),
+                 "r"(lanes_off[3]), "r"(lanes_off[4]), "r"(lanes_off[5]), "r"(lanes_off[6]), "r"(lanes_off[7]) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_elect(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+               "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
+               ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
 // Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a 128B-swizzled panel.
 __device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
 

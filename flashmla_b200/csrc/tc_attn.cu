@@ -661,12 +661,15 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   if (__any_sync(0xffffffffu, clipped) && lane == 0 && c.status) atomicCAS(c.status, 0, FMLA_STATUS_CLIPPED);
 }
 
-// ---- MMA issuers (one thread each, CTA 0) ---------------------------------------------------------
+// ---- MMA issuers (one warp each, CTA 0) ---------------------------------------------------------
+// An issuer is a whole warp that stays converged: every lane waits on the barriers and computes the same descriptors,
+// and one elected lane issues (see umma_ts_pair_elect for why).
 // QK^T issuer k writes S buffer k: it takes the blocks whose running number has parity k, so consecutive blocks are
-// issued by two threads and the instruction issue of one overlaps the other's; a block's 20 products still come from
+// issued by two warps and the instruction issue of one overlaps the other's; a block's 20 products still come from
 // one thread in a fixed order, which keeps the results bitwise repeatable.
 template <class P>
 __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem, uint32_t k) {
+  constexpr uint32_t ALL = 0xffffffffu;
   // decode: NoPE k-steps are fp16 x fp16 (Q converted on load, K dequantised to fp16); RoPE k-steps are bf16
   const uint32_t idesc_nope = p.mode == 0 ? idesc_16bit(128, 2 * T, 0, 0, false, false) : idesc_bf16(128, 2 * T, false, false);
   constexpr uint32_t idesc_rope = idesc_bf16(128, 2 * T, false, false);
@@ -680,25 +683,25 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
   Item it;
   uint32_t seq = 0;
   for (int i = 0; get_item(p, rec, i, it); ++i) {
-    if (!wait(c, Q_FULL, i, 21)) return;
+    if (!__all_sync(ALL, wait(c, Q_FULL, i, 21))) return;
     const uint32_t seq_end = seq + (uint32_t)num_blocks(it);
     for (seq += (seq ^ k) & 1u; seq < seq_end; seq += 2) {
       const uint32_t pos = seq + 2u * (uint32_t)(i + 1);       // ring position: two per item hold its Q
       const int s = pos % nst;
-      if (!wait(c, KV_FULL + s, pos / nst, 22)) return;
-      if (seq >= 2 && !wait(c, S_EMPTY + k, (seq >> 1) - 1, 23)) return;
+      if (!__all_sync(ALL, wait(c, KV_FULL + s, pos / nst, 22))) return;
+      if (seq >= 2 && !__all_sync(ALL, wait(c, S_EMPTY + k, (seq >> 1) - 1, 23))) return;
       tc_fence_after_sync();
       const uint64_t b0 = smem_desc_kmajor(stage_addr(c, s));
       const uint64_t r0 = smem_desc_kmajor_sw64(stage_addr(c, s) + ROPE_PANEL);
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        umma_ts<2>(s_tmem, tmem + TM_Q + 8 * j, b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4), idesc_nope, j > 0);
+        umma_ts_pair_elect(s_tmem, tmem + TM_Q + 8 * j, b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4), idesc_nope, j > 0);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        umma_ss_pair_masked(s_tmem, qr0 + ((j * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_upper);
-        umma_ss_pair_masked(s_tmem, qr0 + (((2 + j) * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_lower);
+        umma_ss_pair_masked_elect(s_tmem, qr0 + ((j * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_upper);
+        umma_ss_pair_masked_elect(s_tmem, qr0 + (((2 + j) * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_lower);
       }
-      umma_commit<2>(bar_addr(c, S_FULL + k), 0x3);
+      umma_commit_pair_elect(bar_addr(c, S_FULL + k), 0x3);
     }
     seq = seq_end;
   }
@@ -706,6 +709,7 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
 
 template <class P>
 __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem) {
+  constexpr uint32_t ALL = 0xffffffffu;
   const uint32_t idesc = p.mode == 0 ? idesc_16bit(128, 256, 0, 0, false, true) : idesc_bf16(128, 256, false, true);
   const int nst = num_stages(p);
   Item it;
@@ -713,12 +717,12 @@ __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint3
   for (int i = 0; get_item(p, rec, i, it); ++i) {
     const int nb = num_blocks(it);
     // the item's first product overwrites O: the epilogue of the item before has read it
-    if (i > 0 && !wait(c, O_FREE, i - 1, 33)) return;
+    if (i > 0 && !__all_sync(ALL, wait(c, O_FREE, i - 1, 33))) return;
     for (int n = 0; n < nb; ++n, ++seq) {
       const uint32_t pos = seq + 2u * (uint32_t)(i + 1);
       const int s = pos % nst, b = seq & 1;
-      if (!wait(c, P_FULL + b, seq >> 1, 31)) return;
-      if (!wait(c, KV_FULL + s, pos / nst, 32)) return;
+      if (!__all_sync(ALL, wait(c, P_FULL + b, seq >> 1, 31))) return;
+      if (!__all_sync(ALL, wait(c, KV_FULL + s, pos / nst, 32))) return;
       tc_fence_after_sync();
       const uint64_t a0 = smem_desc_kmajor(c.base + SM_P + b * P_BYTES);
       const uint64_t v0 = smem_desc_mnmajor(stage_addr(c, s), PANEL);
@@ -726,10 +730,10 @@ __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint3
       for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int ks = 0; ks < T / 16; ++ks)
-          umma_ss<2>(tmem + TM_O + 128 * h, a0 + ((ks * 32) >> 4), v0 + ((h * 2 * PANEL + ks * 2048) >> 4), idesc,
-                     n > 0 || ks > 0);
-      umma_commit<2>(bar_addr(c, KV_EMPTY + s), 0x3);
-      umma_commit<2>(bar_addr(c, PV_DONE + b), 0x3);
+          umma_ss_pair_elect(tmem + TM_O + 128 * h, a0 + ((ks * 32) >> 4), v0 + ((h * 2 * PANEL + ks * 2048) >> 4), idesc,
+                             n > 0 || ks > 0);
+      umma_commit_pair_elect(bar_addr(c, KV_EMPTY + s), 0x3);
+      umma_commit_pair_elect(bar_addr(c, PV_DONE + b), 0x3);
     }
   }
 }
@@ -1255,7 +1259,7 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
     else producer_role(p, rec, c, rank);
   } else if (warp < GATHER_WARP) {
     reg_dec<regs_issuer(MODE)>();
-    if (rank == 0 && (threadIdx.x & 31) == 0) {
+    if (rank == 0) {
       if (warp < PV_WARP) issue_qk(p, rec, c, tmem, (uint32_t)(warp - QK_WARP));
       else if (warp == PV_WARP) issue_pv(p, rec, c, tmem);
     }
