@@ -135,7 +135,8 @@ constexpr uint32_t SM_RAW = SM_STAGE + NSTAGE_DECODE * STAGE_BYTES;
 static_assert(XCHG_BYTES == P_BYTES && SM_LEAVE + 4 <= SM_MASK && SM_XFLAG + NPW * RING <= SM_MAX && SM_MTRUE + 512 <= SM_SUM && SM_IDX + NPW * RING * PROWS * 4 <= SM_P && SM_P % 1024 == 0 &&
               SM_QROPE % 1024 == 0 && SM_STAGE % 1024 == 0 && STAGE_BYTES % 1024 == 0 && SM_RAW % 1024 == 0 && RAW_BYTES % 1024 == 0 && SM_BAR + 8 * NUM_BARS + 12 <= SM_MASK,
               "shared memory map");
-constexpr uint32_t SMEM_USED_PREFILL = SM_STAGE + NSTAGE_PREFILL * STAGE_BYTES;
+constexpr uint32_t SM_XCHG2 = SM_STAGE + NSTAGE_PREFILL * STAGE_BYTES;   // prefill: the second half of the exchange has a buffer of its own
+constexpr uint32_t SMEM_USED_PREFILL = SM_XCHG2 + XCHG_BYTES;
 constexpr uint32_t SMEM_USED_DECODE = SM_RAW + NRAW * RAW_BYTES;
 constexpr uint32_t SMEM_BYTES = (SMEM_USED_PREFILL > SMEM_USED_DECODE ? SMEM_USED_PREFILL : SMEM_USED_DECODE) + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
@@ -433,55 +434,53 @@ __device__ __forceinline__ void dequant_chunk_f16(const uint4& raw, uint32_t sca
 }
 
 // ---- prefill: producer warps --------------------------------------------------------------------------------
-// Producer warp w (of NPW) owns tokens [PROWS*w, PROWS*(w+1)) of every block:
-//   * lanes 0-7 prefetch the tokens' indices into the warp's ring (cp.async, IDX_LOOKAHEAD blocks ahead);
-//   * once the block's stage is free, lane = 5 * group + piece issues one TMA gather of four bf16 rows
-//     (piece = NoPE panel 0-3 / RoPE panel) straight into the swizzled stage.  The warp's arrival and the
-//     gathers' bytes go to the leader CTA's stage barrier, so nobody waits for the landing in between and
-//     the gathers run as far ahead of the MMAs as stages are free.
+// Producer warp w (of NPW) owns tokens [PROWS*w, PROWS*(w+1)) of every block.  Its loop is a chain of dependent
+// shared-memory reads, shuffles and waits around ten gathers, and the eight warps together are the slowest link of the
+// prefill pipeline; so a warp takes two blocks per turn and pays for everything but the gathers once per pair:
+//   * lanes 0-15 prefetch the indices of the pair three turns ahead into the warp's ring (4-byte cp.async), lanes 0-7
+//     those of block 2i and lanes 8-15 those of block 2i+1, each lane with the block cursor of its own block;
+//   * lane = 10 block + 5 group + piece (20 lanes) reads the four indices of its group and, once the block's stage is
+//     free, issues one TMA gather of four bf16 rows (piece = NoPE panel 0-3 / RoPE panel) straight into the swizzled
+//     stage.  The warp's arrival and the gathers' bytes go to the leader CTA's stage barrier, so nobody waits for the
+//     landing in between and the gathers run as far ahead of the MMAs as stages are free.
 template <class P>
 __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank) {
   const int ptid = threadIdx.x - 32 * NSW, pwarp = ptid >> 5, lane = ptid & 31;
   constexpr int nst = NSTAGE_PREFILL;
   const int range = p.s_kv;
   const uint32_t ring = c.base + SM_IDX + (uint32_t)pwarp * (RING * PROWS * 4);
+  static_assert(PROWS == 8 && RING % 2 == 0, "two four-row groups per producer warp and block");
+  const int fsub = (lane >> 3) & 1, frow = lane & 7;  // feeding lanes 0-15: block of the pair, row
   BlockCursor feed(p, rec), gat(p, rec);
+  if (fsub && feed.live) feed.advance(p, rec);        // lanes 8-15 walk the odd blocks
 
-  auto feed_block = [&](uint32_t blk) {       // indices of block blk -> ring slot blk % RING; one cp.async group
-    if (feed.live) {
-      if (lane < PROWS) {
-        const int pos = feed.it.tok_lo + feed.n * T + PROWS * pwarp + lane;
-        const uint32_t dst = ring + ((blk % RING) * PROWS + lane) * 4;
-        if (pos < feed.it.tok_hi && pos < feed.it.limit)
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(feed.it.idx + pos) : "memory");
-        else
-          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0xffffffffu) : "memory");
-      }
+  auto feed_pair = [&](uint32_t j) {          // indices of blocks 2j, 2j+1 -> ring slots (2j + fsub) % RING; one cp.async group
+    if (lane < 2 * PROWS && feed.live) {
+      const int pos = feed.it.tok_lo + feed.n * T + PROWS * pwarp + frow;
+      const uint32_t dst = ring + (((2 * j + fsub) % RING) * PROWS + frow) * 4;
+      if (pos < feed.it.tok_hi && pos < feed.it.limit)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(feed.it.idx + pos) : "memory");
+      else
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0xffffffffu) : "memory");
       feed.advance(p, rec);
+      if (feed.live) feed.advance(p, rec);
     }
     cp_async_commit();
   };
 
 #pragma unroll 1
-  for (int k = 0; k < IDX_LOOKAHEAD; ++k) feed_block(k);
-  const int q = lane / 5, kind = lane - 5 * q;
-  static_assert(PROWS == 8, "two four-row groups per producer warp");
+  for (int k = 0; k < 3; ++k) feed_pair(k);
+  const int sub = lane / 10, rem = lane - 10 * sub, q = rem / 5, kind = rem - 5 * q;   // issuing lanes 0-19
+  const bool issuer = lane < 20;
   uint32_t pos = 0;                                   // ring position
-  for (uint32_t g = 0; gat.live; ++g, ++pos, gat.advance(p, rec)) {
-    if (gat.n == 0 && !fill_q_positions(p, c, rank, pwarp, lane, gat.item, gat.it.req, 0, pos)) return;
-    // groups 0 .. g+IDX_LOOKAHEAD-1 are committed; with at most IDX_LOOKAHEAD-1 pending, group g has landed
-    cp_async_wait<IDX_LOOKAHEAD - 1>();
+  for (uint32_t i = 0; gat.live; ++i) {
+    // pairs 0 .. i+2 are committed; with at most two groups pending, pair i has landed
+    cp_async_wait<2>();
     __syncwarp();
-    const int st = pos % nst;
-    const uint32_t use = pos / nst;
-    bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 12);
-    if (!__all_sync(0xffffffffu, ok)) return;
-    const uint32_t dst = stage_addr(c, st);
-    const uint32_t bar = map_to_cta(bar_addr(c, KV_FULL + st), 0);      // shared::cluster address of the leader's stage barrier
     uint32_t bits = 0;
     int id[4] = {-1, -1, -1, -1};
-    if (q < PROWS / 4) {
-      const uint4 v = lds_16(ring + ((g % RING) * PROWS + 4 * q) * 4);
+    if (issuer) {
+      const uint4 v = lds_16(ring + (((2 * i + sub) % RING) * PROWS + 4 * q) * 4);
       id[0] = (int)v.x; id[1] = (int)v.y; id[2] = (int)v.z; id[3] = (int)v.w;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -489,20 +488,31 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
         if (kind == 0) bits |= 1u << (4 * q + k);                       // one lane per group reports validity
       }
     }
-    bits |= __shfl_xor_sync(0xffffffffu, bits, 5);                     // lanes 0 and 5 hold the two groups
-    if (lane == 0) {
-      asm volatile("st.shared.u8 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (g % RING) + pwarp), "r"(bits) : "memory");
-      mbar_expect_tx_cluster(bar, STAGE_TX_BYTES / NPW);               // after the mask store
+    bits |= __shfl_xor_sync(0xffffffffu, bits, 5);                     // lanes 0 / 10 hold the two groups of block 0 / 1
+#pragma unroll 1
+    for (int s = 0; s < 2 && gat.live; ++s, ++pos, gat.advance(p, rec)) {
+      const uint32_t g = 2 * i + s;
+      if (gat.n == 0 && !fill_q_positions(p, c, rank, pwarp, lane, gat.item, gat.it.req, 0, pos)) return;
+      const int st = pos % nst;
+      const uint32_t use = pos / nst;
+      const bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 12);
+      if (!__all_sync(0xffffffffu, ok)) return;
+      const uint32_t dst = stage_addr(c, st);
+      const uint32_t bar = map_to_cta(bar_addr(c, KV_FULL + st), 0);      // shared::cluster address of the leader's stage barrier
+      if (lane == 10 * s) {
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (g % RING) + pwarp), "r"(bits) : "memory");
+        mbar_expect_tx_cluster(bar, STAGE_TX_BYTES / NPW);               // after the mask store
+      }
+      __syncwarp();
+      if (issuer && sub == s) {
+        const uint32_t r0 = (uint32_t)PROWS * pwarp + 4u * q;             // first of the four stage rows
+        const uint32_t d = kind < 4 ? dst + kind * PANEL + r0 * 128u : dst + ROPE_PANEL + r0 * 64u;
+        const CUtensorMap* map = kind < 4 ? &p.map_nope : &p.map_rope;
+        const int col = kind < 4 ? 256 * (int)rank + 64 * kind : 512 + 32 * (int)rank;
+        tma_gather4_pair(map_to_cta(d, rank), map, col, make_int4(id[0], id[1], id[2], id[3]), bar);
+      }
     }
-    __syncwarp();
-    if (q < PROWS / 4) {
-      const uint32_t r0 = (uint32_t)PROWS * pwarp + 4u * q;             // first of the four stage rows
-      const uint32_t d = kind < 4 ? dst + kind * PANEL + r0 * 128u : dst + ROPE_PANEL + r0 * 64u;
-      const CUtensorMap* map = kind < 4 ? &p.map_nope : &p.map_rope;
-      const int col = kind < 4 ? 256 * (int)rank + 64 * kind : 512 + 32 * (int)rank;
-      tma_gather4_pair(map_to_cta(d, rank), map, col, make_int4(id[0], id[1], id[2], id[3]), bar);
-    }
-    feed_block(g + IDX_LOOKAHEAD);
+    feed_pair(i + 3);
   }
   cp_async_wait<0>();
 }
@@ -768,6 +778,20 @@ __device__ __noinline__ void leave_group(uint32_t leave_word, int warp) {
   }
 }
 
+// packed fp32 arithmetic (two lanes per instruction): the softmax chain is bound by the instructions it issues
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 r;
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return r;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 r;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return r;
+}
 // running maximum of |x| over packed bf16 pairs
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
   uint32_t r;
@@ -889,11 +913,13 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   // as [head range h / 32][receiving half][32 heads][16 floats]: the 4 KB of a head range are exactly the P rows of the
   // same 32 heads, so only the two warps of a pair ever touch them, in the exchange as well as when P is written.  The
   // 16-byte chunk k of a 64-byte row sits at chunk position k ^ ((row / 2) % 4): eight consecutive rows then cover all
-  // bank groups.
+  // bank groups.  (Decode has no shared memory to spare for this; prefill has, and gives the second half a buffer like
+  // the first one, so that a block need not wait at its start for the PV product that read the P buffer last.)
   const uint32_t xoff = 4096u * (uint32_t)(h >> 5) + 64u * (uint32_t)(h & 31);
   const uint32_t xput = 2048u * (uint32_t)(1 - half) + xoff, xget = 2048u * (uint32_t)half + xoff;
   const uint32_t xsw = ((uint32_t)h >> 1) & 3u;
   const uint32_t pbuf = c.base + SM_P + team * P_BYTES, xbuf = c.base + SM_XCHG;
+  const uint32_t xbuf2 = p.mode == 0 ? pbuf : c.base + SM_XCHG2;
   const uint32_t max_mine = c.base + SM_MAX + 4u * (64 * slot + h), max_mate = c.base + SM_MAX + 4u * (64 * (slot ^ 1) + h);
   const uint32_t mref_mine = c.base + SM_MREF + 4u * (64 * team + h), mref_other = c.base + SM_MREF + 4u * (64 * (team ^ 1) + h);
   const uint32_t sum_base = c.base + SM_SUM + 4u * h, mtrue_base = c.base + SM_MTRUE + 4u * h;
@@ -940,9 +966,9 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       bool ok = wait(c, S_FULL + team, seq >> 1, 41);
       // the other team has finished with the exchange buffer and has settled the reference maximum of block seq - 1
       ok = ok && (seq == 0 || wait(c, DEC + (team ^ 1), (seq - 1) >> 1, 42));
-      // the PV product that read this team's P buffer last has completed (it did so about a block ago): the buffer
-      // carries half of the exchange now and the block's probabilities later
-      ok = ok && (seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45));
+      // decode: the PV product that read this team's P buffer last has completed (it did so about a block ago): the
+      // buffer carries half of the exchange now and the block's probabilities later
+      if (p.mode == 0) ok = ok && (seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45));
       if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
       tc_fence_after_sync();
       // of the block's 64 tokens this thread finishes 32 (tokens 32*half ..): it reads its own partial dot
@@ -954,7 +980,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          st_shared16((k < 4 ? xbuf : pbuf) + xput + (((uint32_t)(k & 3) ^ xsw) << 4),
+          st_shared16((k < 4 ? xbuf : xbuf2) + xput + (((uint32_t)(k & 3) ^ xsw) << 4),
                       make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
       }
       tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * half, keep);
@@ -966,11 +992,10 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       float x[32];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint4 t = lds_16((k < 4 ? xbuf : pbuf) + xget + (((uint32_t)(k & 3) ^ xsw) << 4));
-        x[4 * k] = __uint_as_float(keep[4 * k]) + __uint_as_float(t.x);
-        x[4 * k + 1] = __uint_as_float(keep[4 * k + 1]) + __uint_as_float(t.y);
-        x[4 * k + 2] = __uint_as_float(keep[4 * k + 2]) + __uint_as_float(t.z);
-        x[4 * k + 3] = __uint_as_float(keep[4 * k + 3]) + __uint_as_float(t.w);
+        const uint4 t = lds_16((k < 4 ? xbuf : xbuf2) + xget + (((uint32_t)(k & 3) ^ xsw) << 4));
+        const float2 lo = add2(make_float2(__uint_as_float(keep[4 * k]), __uint_as_float(keep[4 * k + 1])), make_float2(__uint_as_float(t.x), __uint_as_float(t.y)));
+        const float2 hi = add2(make_float2(__uint_as_float(keep[4 * k + 2]), __uint_as_float(keep[4 * k + 3])), make_float2(__uint_as_float(t.z), __uint_as_float(t.w)));
+        x[4 * k] = lo.x; x[4 * k + 1] = lo.y; x[4 * k + 2] = hi.x; x[4 * k + 3] = hi.y;
       }
       const uint32_t vmask = lds_u32(c.base + SM_MASK + 8u * (seq % RING) + 4u * half);
       float mx = -CUDART_INF_F;
@@ -996,9 +1021,11 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_addr(c, DEC + team));
       if (__any_sync(0xffffffffu, bump && alpha != 0.f)) {   // rescale this lane's 256 columns of O
-        // every PV product issued so far must have completed (this team's previous one has, see the top of the
-        // block, so the parity of the other team's barrier cannot be mistaken for the completion before)
-        ok = wait(c, PV_DONE + (team ^ 1), (seq - 1) >> 1, 44);
+        // every PV product issued so far must have completed.  This team's previous one first (decode has waited for it
+        // at the top of the block): then the product before that one has completed too, and the parity of the other
+        // team's barrier cannot be mistaken for that earlier completion
+        ok = p.mode == 0 || seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
+        ok = ok && wait(c, PV_DONE + (team ^ 1), (seq - 1) >> 1, 44);
         if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
         tc_fence_after_sync();
 #pragma unroll 1
@@ -1017,18 +1044,24 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       // p = 2^(x * scale - m_ref); while no valid token has been seen every x is -inf and the offset is 0, so p = 0
       const float off = m_new == -CUDART_INF_F ? 0.f : -m_new;
       uint32_t pk[16];
-      float sum = 0.f;
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), off2 = make_float2(off, off);
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float p0 = exp2f(fmaf(x[2 * j], p.scale_log2, off));
-        const float p1 = exp2f(fmaf(x[2 * j + 1], p.scale_log2, off));
-        sum += p0 + p1;
-        pk[j] = p.mode == 0 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+        const float2 a = fma2(make_float2(x[2 * j], x[2 * j + 1]), scale2, off2);
+        const float2 e = make_float2(exp2f(a.x), exp2f(a.y));
+        sum2[j & 1] = add2(sum2[j & 1], e);
+        pk[j] = p.mode == 0 ? pack_f16x2(e.x, e.y) : pack_bf16x2(e.x, e.y);
       }
-      l_sum += sum;
+      l_sum += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
 
       // P rows of these 32 heads overwrite the pair's exchange data in the buffer: the pair barrier above (row maxima)
-      // lies between the mate's reads of that data and these stores
+      // lies between the mate's reads of that data and these stores.  Prefill has not waited yet for the PV product that
+      // read the buffer last.
+      if (p.mode != 0) {
+        ok = seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
+        if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
+      }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         st_shared16(pbuf + swz(h, 4 * half + k), make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]));
