@@ -59,7 +59,7 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures summarised under profiles/
 # (captured on the reduced cases c2s / c4s / c5s and scaled by the units a full launch processes)
-NCU_TRAFFIC = {"c2": 411.5e6, "c2s": 51.43e6, "c4": 1.30e9, "c4s": 188.2e6}
+NCU_TRAFFIC = {"c2": 424.2e6, "c2s": 53.03e6, "c4": 1.32e9, "c4s": 190.7e6}
 METRIC = {"decode": "fp8_sparse_mla_decode_tflops", "prefill_fwd": "sparse_prefill_fwd_tflops",
           "prefill_bwd": "sparse_prefill_bwd_tflops"}
 KERNEL_NAME = {"decode": "pair_attn_kernel<0,0>", "prefill_fwd": "pair_attn_kernel<1,0>",
