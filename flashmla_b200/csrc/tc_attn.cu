@@ -977,14 +977,13 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       {
         uint32_t send[32];
         tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * (1 - half), send);
+        tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * half, keep);      // both loads in flight together
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           st_shared16((k < 4 ? xbuf : xbuf2) + xput + (((uint32_t)(k & 3) ^ xsw) << 4),
                       make_uint4(send[4 * k], send[4 * k + 1], send[4 * k + 2], send[4 * k + 3]));
       }
-      tmem_ld32(tmem_lane + TM_S + 64 * team + 32 * half, keep);
-      tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) arrive_leader(c, S_EMPTY + team);
