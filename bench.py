@@ -10,7 +10,7 @@ combine kernel; the tile scheduler's output is cached after the first call, as i
 own timing, tests/kernelkit/bench.py:77-100).  Prints ONE JSON line on rank 0.
 
 On one GPU the default run also measures the other benchmark configurations for a few steps each
-(MXFP8 decode "c3", prefill forward "c4", prefill backward "c5") and reports them under "also".
+(MXFP8 decode "c3", MODEL1 decode "m1", prefill forward "c4", prefill backward "c5") and reports them under "also".
 
 Multi-GPU (launched by torch.distributed.run): every rank owns its own sequences and KV pages
 (decode) or its own query tokens (prefill); there is no collective in the data path.  The headline is
@@ -46,6 +46,9 @@ WORKLOADS = {
                name="mxfp8_sparse_decode_b256_sq1_h128_topk2048_sk65536"),
     "c4": dict(kind="prefill_fwd", s_q=4096, s_kv=32768, h_q=128, topk=2048, offset=28672,
                name="sparse_prefill_fwd_sq4096_skv32768_h128_topk2048"),
+    # the c2 shape with the reference's second model shape: d_qk = 512, MODEL1 cache blocks
+    "m1": dict(kind="decode", b=128, s_q=2, h_q=128, topk=2048, lo=4096, hi=32768, layout=wl.LAYOUT_MODEL1,
+               name="fp8_sparse_decode_model1_d512_b128_sq2_h128_topk2048_sk4096-32768"),
     # reduced copies of c2 / c4 for profiler captures (same kernels and per-unit work, fewer units; inputs still exceed L2)
     "c2s": dict(kind="decode", b=16, s_q=2, h_q=128, topk=2048, lo=4096, hi=32768, layout=wl.LAYOUT_V32,
                 name="fp8_sparse_decode_v32_b16_sq2_h128_topk2048_sk4096-32768"),
@@ -435,8 +438,8 @@ def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
                 "note": "the whole step (all launches), 2*h_q*topk*(3*576+2*512) flops per query token"}
     return {"bound": "tensor", "achieved": bench.flops / t_kernel / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
             "frac": bench.flops / t_kernel / 1e12 / pk["bf16_tflops"], "traffic": NCU_TRAFFIC.get(key), "basis": pk["basis"],
-            "kernel": KERNEL_NAME[bench.kind], "ms_per_launch": t_kernel * 1e3,
-            "note": "the attention kernel alone (one launch per step), 2*h_q*topk*(576+512) flops per query token; "
+            "kernel": "pair_attn_kernel<0,2>" if key == "m1" else KERNEL_NAME[bench.kind], "ms_per_launch": t_kernel * 1e3,
+            "note": "the attention kernel alone (one launch per step), 2*h_q*topk*(d_qk+512) flops per query token; "
                     "traffic = DRAM bytes of one launch from the ncu capture under profiles/"}
 
 
@@ -574,7 +577,7 @@ def main():
             # ---- the other benchmark configurations, a few steps each
             del bench
             also = {}
-            for key, steps in (("c3", 6), ("c4", 3), ("c5", 2)):
+            for key, steps in (("c3", 6), ("m1", 6), ("c4", 3), ("c5", 2)):
                 torch.cuda.empty_cache()
                 c = WORKLOADS[key]
                 ob = Bench(c, dev, args.seed + 7)

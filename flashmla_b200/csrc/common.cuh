@@ -117,6 +117,11 @@ __device__ __forceinline__ uint4 ldg_nc_16(const void* p) {
                : "l"(p));
   return v;
 }
+__device__ __forceinline__ uint2 ldg_nc_8(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
 #endif
 
 }  // namespace fmla

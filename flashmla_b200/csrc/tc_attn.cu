@@ -93,6 +93,11 @@ constexpr uint32_t STAGE_TX_BYTES = T * (512 + 64);
 constexpr uint32_t RAW_NOPE = 0, RAW_SCALE = T * 256, SCALE_GROUP = 128, RAW_ROPE = RAW_SCALE + (T / 4) * SCALE_GROUP, ROPE_GROUP = 256;
 constexpr uint32_t RAW_BYTES = (RAW_ROPE + (T / 4) * ROPE_GROUP + 1023) / 1024 * 1024;
 constexpr uint32_t RAW_TX_BYTES = GROWS * (256 + 16 + 64);      // bytes one gather warp brings per block
+// raw slot, MODEL1 (d_qk = 512: a row is 448 e4m3 + 64 bf16, and CTA r owns values [256r, 256r+256) of it): CTA 0 holds
+// 64 rows x 256 e4m3 bytes, CTA 1 64 rows x 192 e4m3 bytes and then 64 rows x 128 bytes of bf16; then, in both, the rows'
+// eight scale bytes (seven e8m0, one per 64 values), which the gather warps fetch with plain loads
+constexpr uint32_t M1_RAW_ROPE = T * 192, M1_RAW_SCALE = M1_RAW_ROPE + T * 128;
+static_assert(M1_RAW_SCALE + T * 8 <= RAW_BYTES && M1_RAW_SCALE >= T * 256, "MODEL1 raw slot");
 constexpr uint32_t P_BYTES = 64 * 128;
 constexpr uint32_t QROPE_BYTES = 64 * 128;          // Q's RoPE part of this CTA's 64 heads: one 128B-swizzled [64 x 64] panel
 // tensor memory: O | Q (NoPE half of the lane: 256 dims, two per column) | two S buffers
@@ -143,6 +148,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
 
 struct Params {
   CUtensorMap map_nope, map_rope;   // decode: byte views of the pool (256-byte NoPE box, 64-byte RoPE box); prefill: bf16 views of kv (64 / 32 dims)
+                                    // MODEL1 decode: 576-byte-pitch views with boxes of 256 (map_nope), 192 (map_rope) and 128 bytes (map_nope2)
   CUtensorMap map_scale;            // decode: byte view of the pool with a 16-byte box (the scale field of a row)
   CUtensorMap map_nope2, map_rope2, map_scale2;   // the same for the extra cache
   CUtensorMap map_q;               // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle)
@@ -192,10 +198,12 @@ struct Params {
 };
 // Params with the mode as a compile-time constant: `p.mode` in the device code below resolves to it, so each
 // instantiation of the kernel carries the code of one mode only.
-template <int MODE, int EXTRA>
+// VARIANT (decode): 0 = one cache of 656-byte rows, 1 = two such caches, 2 = one cache of MODEL1 blocks (d_qk = 512)
+template <int MODE, int VARIANT>
 struct ParamsT : Params {
   static constexpr int mode = MODE;
-  static constexpr int has_extra = EXTRA;     // decode over two caches; a compile-time constant like the mode
+  static constexpr int has_extra = VARIANT == 1;     // decode over two caches; a compile-time constant like the mode
+  static constexpr int m1 = VARIANT == 2;            // MODEL1 rows: 448 e4m3 + 64 bf16, V = all 512 values
 };
 
 struct Item {
@@ -433,6 +441,20 @@ __device__ __forceinline__ void dequant_chunk_f16(const uint4& raw, uint32_t sca
   out_hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+// running maximum of |x| over packed bf16 pairs
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(acc), "r"(v));
+  return r;
+}
+// whether a packed pair of non-negative bf16 holds a value beyond fp16's largest (65504; the next bf16 is 65536 = 0x4780)
+__device__ __forceinline__ bool beyond_f16(uint32_t absmax) { return (((absmax & 0x7fff7fffu) + 0x38803880u) & 0x80008000u) != 0u; }
+// bf16 pair -> fp16 pair (values beyond fp16's range saturate to +-65504)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(v & 0xffff0000u)), "f"(__uint_as_float(v << 16)));
+  return r;
+}
 // ---- prefill: producer warps --------------------------------------------------------------------------------
 // Producer warp w (of NPW) owns tokens [PROWS*w, PROWS*(w+1)) of every block.  Its loop is a chain of dependent
 // shared-memory reads, shuffles and waits around ten gathers, and the eight warps together are the slowest link of the
@@ -560,20 +582,47 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
 #pragma unroll 1
   for (int k = 0; k < IDX_LOOKAHEAD; ++k) feed_block(k);
   const int grp = lane & 3, piece = lane >> 2;
-  for (uint32_t g = 0; g < total_blocks; ++g) {
-    // groups 0 .. g+IDX_LOOKAHEAD-1 are committed; with at most IDX_LOOKAHEAD-1 pending, group g has landed
+  // MODEL1: row lane % 16 of block blk as a row number of the pool's 576-byte-pitch view (-1: invalid slot), and the
+  // row's eight scale bytes, which sit behind the block's data rows: read with a plain load one block ahead of the
+  // gathers and stored into the raw slot by this warp (zero for an invalid slot: its data bytes are zero-filled)
+  auto m1_row = [&](uint32_t blk, uint2& scales) -> int {
+    scales = make_uint2(0u, 0u);
+    if (blk >= total_blocks) return -1;
+    const int id = (int)lds_u32(ring + ((blk % RING) * GROWS + (lane & 15)) * 4);
+    if (id < 0 || id >= p.total_rows) return -1;
+    const int b = id / p.page, off = id - b * p.page;
+    scales = ldg_nc_8(p.kv_rows + (int64_t)b * p.kv_stride_block + (int64_t)p.page * M1_DATA_BYTES + off * 8);
+    return b * p.rows_per_block + off;
+  };
+  uint2 m1_scales = make_uint2(0u, 0u);
+  int m1_vrow = -1;
+  if (p.m1) {
     cp_async_wait<IDX_LOOKAHEAD - 1>();
+    __syncwarp();
+    m1_vrow = m1_row(0, m1_scales);
+  }
+  for (uint32_t g = 0; g < total_blocks; ++g) {
+    // groups 0 .. g+IDX_LOOKAHEAD-1 are committed; with at most IDX_LOOKAHEAD-1 pending, group g has landed (MODEL1
+    // looks one block further)
+    if (p.m1) cp_async_wait<IDX_LOOKAHEAD - 2>(); else cp_async_wait<IDX_LOOKAHEAD - 1>();
     __syncwarp();
     bool extra = false;
     if (p.has_extra) { uint32_t f; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(f) : "r"(flags + g % RING)); extra = f != 0; }
-    const int64_t total = extra ? p.total_rows2 : p.total_rows;
-    const int page = extra ? p.page2 : p.page, rpb = extra ? p.rows_per_block2 : p.rows_per_block;
-    // row lane % 16 of the warp as a row number of the pool's 656-byte-pitch view (a cache block may be padded by whole rows)
-    const int id = (int)lds_u32(ring + ((g % RING) * GROWS + (lane & 15)) * 4);
     int vrow = -1;
-    if (id >= 0 && id < total) {
-      if (rpb == page) vrow = id;
-      else { const int b = id / page; vrow = b * rpb + (id - b * page); }
+    uint2 m1_scales_next = make_uint2(0u, 0u);
+    int m1_vrow_next = -1;
+    if (p.m1) {
+      vrow = m1_vrow;
+      m1_vrow_next = m1_row(g + 1, m1_scales_next);
+    } else {
+      const int64_t total = extra ? p.total_rows2 : p.total_rows;
+      const int page = extra ? p.page2 : p.page, rpb = extra ? p.rows_per_block2 : p.rows_per_block;
+      // row lane % 16 of the warp as a row number of the pool's 656-byte-pitch view (a cache block may be padded by whole rows)
+      const int id = (int)lds_u32(ring + ((g % RING) * GROWS + (lane & 15)) * 4);
+      if (id >= 0 && id < total) {
+        if (rpb == page) vrow = id;
+        else { const int b = id / page; vrow = b * rpb + (id - b * page); }
+      }
     }
     const uint32_t bits = __ballot_sync(0xffffffffu, vrow >= 0) & 0xffffu;
     int4 rows;
@@ -586,13 +635,30 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
     const bool ok = use == 0 || wait(c, RAW_EMPTY + gw * NRAW + slot, use - 1, 12);
     if (!__all_sync(0xffffffffu, ok)) return;
     const uint32_t bar = bar_addr(c, RAW_FULL + gw * NRAW + slot);
+    const uint32_t dst = c.base + SM_RAW + (uint32_t)slot * RAW_BYTES;
+    const uint32_t q = (uint32_t)(4 * gw + grp);                   // group of four rows within the block
+    if (p.m1) {
+      if (lane < GROWS)
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst + M1_RAW_SCALE + (uint32_t)(GROWS * gw + lane) * 8u), "r"(m1_scales.x), "r"(m1_scales.y) : "memory");
+      if (lane == 0) asm volatile("st.shared.u16 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (g % RING) + 2u * gw), "r"(bits) : "memory");
+      __syncwarp();                   // the stores above happen before the arrival below
+      if (lane == 0) mbar_expect_tx(bar, GROWS * (rank == 0 ? 256u : 320u));
+      if (rank == 0) {
+        if (piece == 0) tma_gather4(dst + q * 1024u, &p.map_nope, 0, rows, bar);
+      } else {
+        if (piece == 0) tma_gather4(dst + q * 768u, &p.map_rope, 256, rows, bar);
+        else if (piece == 1) tma_gather4(dst + M1_RAW_ROPE + q * 512u, &p.map_nope2, M1_D_NOPE, rows, bar);
+      }
+      m1_vrow = m1_vrow_next;
+      m1_scales = m1_scales_next;
+      feed_block(g + IDX_LOOKAHEAD);
+      continue;
+    }
     if (lane == 0) {
       asm volatile("st.shared.u16 [%0], %1;" ::"r"(c.base + SM_MASK + 8u * (g % RING) + 2u * gw), "r"(bits) : "memory");
       mbar_expect_tx(bar, RAW_TX_BYTES);
     }
     __syncwarp();
-    const uint32_t dst = c.base + SM_RAW + (uint32_t)slot * RAW_BYTES;
-    const uint32_t q = (uint32_t)(4 * gw + grp);                   // group of four rows within the block
     if (piece == 0) tma_gather4(dst + RAW_NOPE + q * 1024u, extra ? &p.map_nope2 : &p.map_nope, 256 * (int)rank, rows, bar);
     else if (piece == 1) tma_gather4(dst + RAW_ROPE + q * ROPE_GROUP, extra ? &p.map_rope2 : &p.map_rope, ROPE_OFF + 64 * (int)rank, rows, bar);
     else if (piece == 2) tma_gather4(dst + RAW_SCALE + q * SCALE_GROUP, extra ? &p.map_scale2 : &p.map_scale, SCALE_OFF, rows, bar);
@@ -628,21 +694,47 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     const uint32_t raw = c.base + SM_RAW + (uint32_t)slot * RAW_BYTES, stage = stage_addr(c, st);
     // all loads first, then the arithmetic, then the stores: the shared-memory accesses are ordered among themselves,
     // so this order is what lets the four chunks overlap
-    uint4 in[PROWS / 2];
+    uint4 in[PROWS / 2], in2[PROWS / 2];
     uint32_t sc_bits[PROWS / 2];
+    // MODEL1: the 16 lanes of a row take its 16 chunks of 16 values: all e4m3 in CTA 0; in CTA 1 twelve e4m3 chunks and
+    // four chunks of 16 bf16 values (two 16-byte loads), which only change format
+    const bool m1_bf16 = p.m1 && rank == 1 && ch >= 12;
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
       const uint32_t row = (uint32_t)PROWS * pwarp + 2 * it + (lane >> 4);
-      const uint32_t sc = raw + RAW_SCALE + (row >> 2) * SCALE_GROUP + (row & 3u) * 16u;
-      in[it] = lds_16(raw + RAW_NOPE + row * 256u + ch * 16u);
-      if (p.layout == FMLA_LAYOUT_V32) sc_bits[it] = lds_u32(sc + 4u * (2u * rank + (ch >> 3)));
-      else asm volatile("ld.shared.u8 %0, [%1];" : "=r"(sc_bits[it]) : "r"(sc + 8u * rank + (ch >> 1)));
+      if (p.m1) {
+        if (m1_bf16) {
+          in[it] = lds_16(raw + M1_RAW_ROPE + row * 128u + (ch - 12) * 32u);
+          in2[it] = lds_16(raw + M1_RAW_ROPE + row * 128u + (ch - 12) * 32u + 16u);
+          sc_bits[it] = 127u;
+        } else {
+          in[it] = lds_16(raw + row * (rank == 0 ? 256u : 192u) + ch * 16u);
+          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(sc_bits[it]) : "r"(raw + M1_RAW_SCALE + row * 8u + 4u * rank + (ch >> 2)));
+        }
+      } else {
+        const uint32_t sc = raw + RAW_SCALE + (row >> 2) * SCALE_GROUP + (row & 3u) * 16u;
+        in[it] = lds_16(raw + RAW_NOPE + row * 256u + ch * 16u);
+        if (p.layout == FMLA_LAYOUT_V32) sc_bits[it] = lds_u32(sc + 4u * (2u * rank + (ch >> 3)));
+        else asm volatile("ld.shared.u8 %0, [%1];" : "=r"(sc_bits[it]) : "r"(sc + 8u * rank + (ch >> 1)));
+      }
     }
     const uint32_t rrow = (uint32_t)PROWS * pwarp + (lane >> 2), chr = lane & 3;
-    const uint4 rope = lds_16(raw + RAW_ROPE + (rrow >> 2) * ROPE_GROUP + (rrow & 3u) * 64u + chr * 16u);
+    uint4 rope = make_uint4(0u, 0u, 0u, 0u);
+    if (!p.m1) rope = lds_16(raw + RAW_ROPE + (rrow >> 2) * ROPE_GROUP + (rrow & 3u) * 64u + chr * 16u);
     uint4 lo[PROWS / 2], hi[PROWS / 2];
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
+      if (m1_bf16) {          // bf16 -> fp16: values beyond fp16's range saturate and are reported
+        uint32_t amax = 0;
+        const uint32_t w[8] = {in[it].x, in[it].y, in[it].z, in[it].w, in2[it].x, in2[it].y, in2[it].z, in2[it].w};
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { amax = absmax_bf16x2(amax, w[k]); o[k] = bf16x2_to_f16x2(w[k]); }
+        clipped |= beyond_f16(amax);
+        lo[it] = make_uint4(o[0], o[1], o[2], o[3]);
+        hi[it] = make_uint4(o[4], o[5], o[6], o[7]);
+        continue;
+      }
       const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(sc_bits[it]) : e8m0_to_float(sc_bits[it]);
       clipped |= scale > MAX_STAGED_SCALE;
       dequant_chunk_f16(in[it], scale_to_half2(scale), lo[it], hi[it]);
@@ -658,7 +750,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       st_shared16(panel + swz(row, 2 * (ch & 3)), lo[it]);
       st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi[it]);
     }
-    st_shared16(stage + ROPE_PANEL + rrow * 64u + ((chr ^ ((rrow >> 1) & 3u)) << 4), rope);
+    if (!p.m1) st_shared16(stage + ROPE_PANEL + rrow * 64u + ((chr ^ ((rrow >> 1) & 3u)) << 4), rope);
     // the dequantised rows (generic proxy) become visible to the MMAs, and this warp's reads of the raw slot
     // are ordered before the TMA writes of the slot's next use
     fence_async_smem();
@@ -706,10 +798,12 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
 #pragma unroll
       for (int j = 0; j < 16; ++j)
         umma_ts_pair_elect(s_tmem, tmem + TM_Q + 8 * j, b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4), idesc_nope, j > 0);
+      if (!p.m1) {            // a MODEL1 row is its 512 values: the RoPE part is among them, as fp16
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        umma_ss_pair_masked_elect(s_tmem, qr0 + ((j * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_upper);
-        umma_ss_pair_masked_elect(s_tmem, qr0 + (((2 + j) * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_lower);
+        for (int j = 0; j < 2; ++j) {
+          umma_ss_pair_masked_elect(s_tmem, qr0 + ((j * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_upper);
+          umma_ss_pair_masked_elect(s_tmem, qr0 + (((2 + j) * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_lower);
+        }
       }
       umma_commit_pair_elect(bar_addr(c, S_FULL + k), 0x3);
     }
@@ -790,20 +884,6 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\t"
       "mov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return r;
-}
-// running maximum of |x| over packed bf16 pairs
-__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
-  uint32_t r;
-  asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(acc), "r"(v));
-  return r;
-}
-// whether a packed pair of non-negative bf16 holds a value beyond fp16's largest (65504; the next bf16 is 65536 = 0x4780)
-__device__ __forceinline__ bool beyond_f16(uint32_t absmax) { return (((absmax & 0x7fff7fffu) + 0x38803880u) & 0x80008000u) != 0u; }
-// bf16 pair -> fp16 pair (values beyond fp16's range saturate to +-65504)
-__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
-  uint32_t r;
-  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(v & 0xffff0000u)), "f"(__uint_as_float(v << 16)));
   return r;
 }
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
@@ -1357,6 +1437,7 @@ static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
 }
 static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
   if (p.mode != 0) return launch_mode<1, 0>(p, grid, stream);
+  if (p.layout == FMLA_LAYOUT_MODEL1) return launch_mode<0, 2>(p, grid, stream);
   return p.has_extra ? launch_mode<0, 1>(p, grid, stream) : launch_mode<0, 0>(p, grid, stream);
 }
 
@@ -1393,7 +1474,9 @@ bool tc_decode_supported(const FmlaDecodeArgs& a) {
   auto pool_ok = [](int64_t stride, int64_t blocks, int64_t page) {
     return stride % ROW_BYTES == 0 && (uint64_t)(blocks - 1) * (uint64_t)(stride / ROW_BYTES) + (uint64_t)page <= 0x7fffffffull;
   };
-  if (a.layout == FMLA_LAYOUT_MODEL1) return false;      // the 584-byte block-wise format runs on the CUDA-core kernel
+  if (a.layout == FMLA_LAYOUT_MODEL1)      // data rows at a pitch of 576 bytes; no second cache in this format's kernel variant
+    return a.sm_scale > 0.f && a.extra_kv == nullptr && a.kv_stride_block % M1_DATA_BYTES == 0 &&
+           (uint64_t)(a.num_blocks - 1) * (uint64_t)(a.kv_stride_block / M1_DATA_BYTES) + (uint64_t)a.page_block_size <= 0x7fffffffull;
   if (!(a.sm_scale > 0.f) || !pool_ok(a.kv_stride_block, a.num_blocks, a.page_block_size)) return false;
   return a.extra_kv == nullptr || pool_ok(a.extra_kv_stride_block, a.extra_num_blocks, a.extra_page_block_size);
 }
@@ -1401,14 +1484,17 @@ bool tc_decode_supported(const FmlaDecodeArgs& a) {
 int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   tc::Params p = {};
   p.mode = 0;
-  p.d_qk = D_QK;
+  const bool m1 = a.layout == FMLA_LAYOUT_MODEL1;
+  // MODEL1: q and the cache rows hold 512 values, all of them V.  The kernel treats them as 512 NoPE values (the q map
+  // ends at column 512, so the RoPE tiles read as zero and the RoPE products are skipped).
+  p.d_qk = m1 ? M1_D_QK : D_QK;
   p.h_q = a.h_q; p.topk = a.topk;
   FMLA_REQUIRE(a.sm_scale > 0.f, FMLA_ERR_UNSUPPORTED, "the tensor-core kernel needs a positive softmax scale (got %g); use FMLA_KERNEL_SIMT", (double)a.sm_scale);
   p.scale_log2 = a.sm_scale * LOG2E;
   p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
   p.q_stride0 = a.q_stride_b; p.q_stride1 = a.q_stride_s; p.q_stride_h = a.q_stride_h;
-  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B) &&
-            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B, p.d_qk) &&
+            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 32, CU_TENSOR_MAP_SWIZZLE_64B, p.d_qk);
   p.indices = a.indices; p.idx_stride0 = a.idx_stride_b; p.idx_stride1 = a.idx_stride_s;
   p.topk_length = a.topk_length; p.attn_sink = a.attn_sink;
   p.kv_rows = reinterpret_cast<const uint8_t*>(a.kv);
@@ -1430,8 +1516,17 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   // (the reference has the same requirement, csrc/sm100/decode/head64/kernel.cuh:911-912); tc_decode_supported() tells
   // the caller, which then takes the CUDA-core kernel.
   FMLA_REQUIRE(tc_decode_supported(a), FMLA_ERR_UNSUPPORTED,
-               "sparse_decode: the tensor-core kernel needs KV block strides that are multiples of 656 bytes and at most 2^31 rows "
-               "per cache (got strides %lld / %lld)", (long long)a.kv_stride_block, (long long)a.extra_kv_stride_block);
+               "sparse_decode: the tensor-core kernel needs KV block strides that are multiples of 656 bytes (MODEL1: 576, and no "
+               "extra cache) and at most 2^31 rows per cache (got strides %lld / %lld)", (long long)a.kv_stride_block, (long long)a.extra_kv_stride_block);
+  if (m1) {
+    p.rows_per_block = (int)(a.kv_stride_block / M1_DATA_BYTES);
+    const uint64_t vrows = (uint64_t)(a.num_blocks - 1) * p.rows_per_block + a.page_block_size;
+    if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 192, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    if (int rc = tc::make_row_map(&p.map_nope2, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    p.map_rope2 = p.map_rope; p.map_scale = p.map_scale2 = p.map_nope;
+    return tc::launch(p, dim3(2 * a.num_sm_parts, a.s_q, (a.h_q + 127) / 128), stream);
+  }
   p.rows_per_block = (int)(a.kv_stride_block / ROW_BYTES);
   const uint64_t vrows = (uint64_t)(a.num_blocks - 1) * p.rows_per_block + a.page_block_size;
   if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, ROW_BYTES, vrows, ROW_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
