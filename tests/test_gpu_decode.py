@@ -11,6 +11,7 @@ from flashmla_b200 import _lib, workloads as wl
 from oracle import sched as sched_oracle
 from helpers import bf16, load_golden, t
 from gpu_utils import DEV, cu, cu_strided, noncontig, run_decode, oracle_decode, check_decode
+from oracle.compare import assert_north_out
 
 pytestmark = pytest.mark.gpu
 
@@ -286,3 +287,34 @@ def test_model1_against_oracle(case):
     out, lse, _ = run_decode(w)
     ref_out, ref_lse = oracle_decode(w)
     check_decode(out, lse, ref_out, ref_lse)
+
+
+def test_model1_runs_on_the_tensor_core_kernel_and_agrees_with_the_cuda_core_kernel(monkeypatch):
+    """Head counts that are multiples of 64 take the tensor-core variant for MODEL1 blocks (forced here, so that a
+    silent fall-back to the CUDA-core kernel would show as an error), and both kernels give the oracle's answer."""
+    w = wl.make_decode_workload(9, 2, 128, 640, 700, 3000, page=64, layout=wl.LAYOUT_MODEL1, seed=77, invalid_frac=0.02,
+                                with_sink=True, with_topk_length=True, q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55)
+    ref_out, ref_lse = oracle_decode(w)
+    res = {}
+    for kernel in ("tc", "simt"):
+        monkeypatch.setenv("FMLA_KERNEL", kernel)
+        out, lse, _ = run_decode(w)
+        check_decode(out, lse, ref_out, ref_lse)
+        res[kernel] = out.float().cpu()
+    assert_north_out("tc vs simt", res["tc"], res["simt"])
+
+
+def test_model1_rope_values_beyond_fp16_are_reported():
+    """The tensor-core variant stages the 64 bf16 values of a MODEL1 row in fp16 like the rest of the row."""
+    w = wl.make_decode_workload(2, 1, 128, 128, 200, 400, page=64, layout=wl.LAYOUT_MODEL1, seed=78, q_std=1e-4, kv_std=0.1, clamp=1.0)
+    rows = w.kv_rows.contiguous().clone()
+    nb, page = rows.shape[0], rows.shape[1]
+    # the first bf16 value of every token (bytes 448, 449 of its 576 data bytes) becomes 0x4790 = 73728.0
+    flat = rows.reshape(nb, page * 584)
+    data = flat[:, :page * 576].view(nb, page, 576)
+    data[:, :, 448] = 0x90
+    data[:, :, 449] = 0x47
+    import flashmla_b200
+    flash_mla.flash_mla_with_kvcache(cu(w.q), _model1_pool(flat.view(nb, page, 1, 584)), None, None, 512, flash_mla.get_mla_metadata()[0], None,
+                                     w.sm_scale, False, True, cu(w.indices))
+    assert flashmla_b200.kernel_status(DEV) == _lib.STATUS_CLIPPED
