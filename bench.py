@@ -52,6 +52,8 @@ WORKLOADS = {
     # reduced copies of c2 / c4 for profiler captures (same kernels and per-unit work, fewer units; inputs still exceed L2)
     "c2s": dict(kind="decode", b=16, s_q=2, h_q=128, topk=2048, lo=4096, hi=32768, layout=wl.LAYOUT_V32,
                 name="fp8_sparse_decode_v32_b16_sq2_h128_topk2048_sk4096-32768"),
+    "m1s": dict(kind="decode", b=16, s_q=2, h_q=128, topk=2048, lo=4096, hi=32768, layout=wl.LAYOUT_MODEL1,
+                name="fp8_sparse_decode_model1_d512_b16_sq2_h128_topk2048_sk4096-32768"),
     "c4s": dict(kind="prefill_fwd", s_q=592, s_kv=32768, h_q=128, topk=2048, offset=28672,
                 name="sparse_prefill_fwd_sq592_skv32768_h128_topk2048"),
     "c5": dict(kind="prefill_bwd", s_q=4096, s_kv=32768, h_q=128, topk=2048, offset=28672,
@@ -438,7 +440,7 @@ def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
                 "note": "the whole step (all launches), 2*h_q*topk*(3*576+2*512) flops per query token"}
     return {"bound": "tensor", "achieved": bench.flops / t_kernel / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
             "frac": bench.flops / t_kernel / 1e12 / pk["bf16_tflops"], "traffic": NCU_TRAFFIC.get(key), "basis": pk["basis"],
-            "kernel": "pair_attn_kernel<0,2>" if key == "m1" else KERNEL_NAME[bench.kind], "ms_per_launch": t_kernel * 1e3,
+            "kernel": "pair_attn_kernel<0,2>" if key in ("m1", "m1s") else KERNEL_NAME[bench.kind], "ms_per_launch": t_kernel * 1e3,
             "note": "the attention kernel alone (one launch per step), 2*h_q*topk*(d_qk+512) flops per query token; "
                     "traffic = DRAM bytes of one launch from the ncu capture under profiles/"}
 
