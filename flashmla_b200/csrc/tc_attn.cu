@@ -671,7 +671,20 @@ template <class P>
 __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t rank) {
   const int ptid = threadIdx.x - 32 * NSW, pwarp = ptid >> 5, lane = ptid & 31;
   const int gw = pwarp / (NPW / NGW);
-  const int ch = lane & 15;
+  // A warp converts its eight rows in four steps of 32 pieces (a piece = 16 values of a row = one 16-byte chunk of e4m3).
+  // Step `it` of a lane is piece (row, chunk): normally two rows per step, 16 lanes per row.  In CTA 1 of a MODEL1 cache
+  // a row has twelve e4m3 chunks and four chunks of 16 bf16 values (two 16-byte loads each), which only change format:
+  // there steps 0-2 take the 96 e4m3 pieces in row order and step 3 the 32 bf16 pieces, so that no step mixes the two.
+  const bool m1_split = p.m1 && rank == 1;
+  auto piece_row = [&](int it) -> uint32_t {
+    if (m1_split) return (uint32_t)PROWS * pwarp + (it < 3 ? (uint32_t)(32 * it + lane) / 12u : (uint32_t)lane >> 2);
+    return (uint32_t)PROWS * pwarp + 2 * it + (lane >> 4);
+  };
+  auto piece_ch = [&](int it) -> uint32_t {
+    if (m1_split) return it < 3 ? (uint32_t)(32 * it + lane) % 12u : 12u + ((uint32_t)lane & 3u);
+    return (uint32_t)lane & 15u;
+  };
+  auto m1_bf16 = [&](int it) { return m1_split && it == 3; };
   uint32_t total_blocks = 0;
   {
     Item it;
@@ -696,14 +709,11 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     // so this order is what lets the four chunks overlap
     uint4 in[PROWS / 2], in2[PROWS / 2];
     uint32_t sc_bits[PROWS / 2];
-    // MODEL1: the 16 lanes of a row take its 16 chunks of 16 values: all e4m3 in CTA 0; in CTA 1 twelve e4m3 chunks and
-    // four chunks of 16 bf16 values (two 16-byte loads), which only change format
-    const bool m1_bf16 = p.m1 && rank == 1 && ch >= 12;
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
-      const uint32_t row = (uint32_t)PROWS * pwarp + 2 * it + (lane >> 4);
+      const uint32_t row = piece_row(it), ch = piece_ch(it);
       if (p.m1) {
-        if (m1_bf16) {
+        if (m1_bf16(it)) {
           in[it] = lds_16(raw + M1_RAW_ROPE + row * 128u + (ch - 12) * 32u);
           in2[it] = lds_16(raw + M1_RAW_ROPE + row * 128u + (ch - 12) * 32u + 16u);
           sc_bits[it] = 127u;
@@ -724,7 +734,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     uint4 lo[PROWS / 2], hi[PROWS / 2];
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
-      if (m1_bf16) {          // bf16 -> fp16: values beyond fp16's range saturate and are reported
+      if (m1_bf16(it)) {      // bf16 -> fp16: values beyond fp16's range saturate and are reported
         uint32_t amax = 0;
         const uint32_t w[8] = {in[it].x, in[it].y, in[it].z, in[it].w, in2[it].x, in2[it].y, in2[it].z, in2[it].w};
         uint32_t o[8];
@@ -745,7 +755,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     if (!__all_sync(0xffffffffu, ok)) return;
 #pragma unroll
     for (int it = 0; it < PROWS / 2; ++it) {
-      const uint32_t row = (uint32_t)PROWS * pwarp + 2 * it + (lane >> 4);
+      const uint32_t row = piece_row(it), ch = piece_ch(it);
       const uint32_t panel = stage + (ch >> 2) * PANEL;
       st_shared16(panel + swz(row, 2 * (ch & 3)), lo[it]);
       st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi[it]);
@@ -798,7 +808,7 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
 #pragma unroll
       for (int j = 0; j < 16; ++j)
         umma_ts_pair_elect(s_tmem, tmem + TM_Q + 8 * j, b0 + (((j >> 2) * PANEL + (j & 3) * 32) >> 4), idesc_nope, j > 0);
-      if (!p.m1) {            // a MODEL1 row is its 512 values: the RoPE part is among them, as fp16
+      if (!p.m1 && p.d_qk == D_QK) {   // rows of 512 values (MODEL1 decode: the RoPE part is among them as fp16; prefill with d_qk = 512: it reads as zero)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           umma_ss_pair_masked_elect(s_tmem, qr0 + ((j * 32) >> 4), r0 + ((j * 32) >> 4), idesc_rope, true, keep_upper);
