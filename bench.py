@@ -425,8 +425,8 @@ def measure(bench: Bench, clk: ClockSampler, steps, warmup, barrier, world, dev,
 
 
 def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
-    """The roofline object of a workload: the tensor pipe bounds all of them (SURVEY of the reference's own
-    flop model: tests/lib.py:345-402)."""
+    """The roofline object of a workload: the tensor pipe bounds all of them (flops counted with the reference's own
+    model, tests/lib.py:345-402)."""
     if bench.kind == "prefill_bwd":
         # t_kernel = the first pass's dQ / dKV launch: its fp32 reductions into dKV are the traffic that matters there
         units = min(bench.units, 592)

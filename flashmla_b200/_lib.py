@@ -19,6 +19,7 @@ KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
 SCHED_META_INTS = 8
 STATIC_SCRATCH_ROWS = 16384
 OPTION_PLAIN_Q_LOADS = 1
+OPTION_PLAIN_STORES = 2
 STATUS_CLIPPED = 100
 
 _i32p = C.POINTER(C.c_int32)

@@ -66,7 +66,7 @@ using namespace fmla;
 
 extern "C" {
 
-int fmla_version(void) { return 130; }   // 130: fmla_set_option, fmla_tensor_map_cache_stats, FMLA_STATUS_* codes
+int fmla_version(void) { return 131; }   // 130: fmla_set_option, fmla_tensor_map_cache_stats, FMLA_STATUS_* codes; 131: FMLA_OPTION_PLAIN_STORES, MODEL1 on the tensor cores
 
 const char* fmla_last_error(void) { return g_error; }
 
@@ -216,6 +216,7 @@ int fmla_sparse_prefill_bwd(const FmlaPrefillBwdArgs* a, void* cuda_stream) {
 
 int fmla_set_option(int option, int value) {
   if (option == FMLA_OPTION_PLAIN_Q_LOADS) { tc_set_plain_q_loads(value); return FMLA_OK; }
+  if (option == FMLA_OPTION_PLAIN_STORES) { tc_set_plain_stores(value); return FMLA_OK; }
   set_error("set_option: unknown option %d", option);
   return FMLA_ERR_INVALID_ARG;
 }

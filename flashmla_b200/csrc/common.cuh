@@ -79,6 +79,7 @@ int launch_simt_prefill_bwd(const FmlaPrefillBwdArgs& a, cudaStream_t stream);
 // tensor-core (tcgen05) kernels
 bool tc_supported(int h_q);
 void tc_set_plain_q_loads(int on);      // diagnostic: Q through plain loads instead of TMA tiles
+void tc_set_plain_stores(int on);       // diagnostic: results through plain stores instead of TMA box stores
 void tc_map_cache_stats(unsigned long long* hits, unsigned long long* misses);
 int tc_decode_plan(int num_sms, int h_q, int s_q, int* num_sm_parts, int* fixed_overhead_blocks, int* block_topk);
 bool tc_decode_supported(const FmlaDecodeArgs& a);      // stride and scale preconditions of the tensor-core decode kernel

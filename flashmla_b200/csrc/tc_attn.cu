@@ -1431,6 +1431,7 @@ static int make_row_map(CUtensorMap* map, const void* base, CUtensorMapDataType 
 // Diagnostic switch (fmla_set_option): read Q with plain loads even when a tensor map could be made, the path that
 // otherwise only runs when the driver refuses q's strides.
 std::atomic<int> g_plain_q_loads{0};
+std::atomic<int> g_plain_stores{0};     // the same for the epilogue: plain stores instead of TMA box stores
 
 template <int MODE, int EXTRA>
 static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
@@ -1441,6 +1442,7 @@ static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
   ParamsT<MODE, EXTRA> pt;
   static_cast<Params&>(pt) = p;
   if (g_plain_q_loads.load(std::memory_order_relaxed)) pt.q_tma = 0;
+  if (g_plain_stores.load(std::memory_order_relaxed)) pt.out_tma = 0;
   pair_attn_kernel<MODE, EXTRA><<<grid, threads_of(MODE), SMEM_BYTES, stream>>>(pt);
   FMLA_CUDA(cudaGetLastError());
   return FMLA_OK;
@@ -1455,6 +1457,7 @@ static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
 
 
 void tc_set_plain_q_loads(int on) { tc::g_plain_q_loads.store(on ? 1 : 0, std::memory_order_relaxed); }
+void tc_set_plain_stores(int on) { tc::g_plain_stores.store(on ? 1 : 0, std::memory_order_relaxed); }
 void tc_map_cache_stats(unsigned long long* hits, unsigned long long* misses) {
   tmap::Cache& c = tmap::cache();
   std::lock_guard<std::mutex> lock(c.mu);

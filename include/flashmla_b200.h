@@ -72,8 +72,11 @@ const char* fmla_last_error(void);
  * Process-wide switches, for diagnosis and tests.  No counterpart in the reference.
  *   FMLA_OPTION_PLAIN_Q_LOADS  non-zero: the tensor-core attention kernel reads Q with plain loads instead of TMA
  *                              tiles (the path it otherwise takes only when the driver refuses q's strides).
+ *   FMLA_OPTION_PLAIN_STORES   non-zero: the tensor-core attention kernel writes its results with plain stores instead
+ *                              of TMA box stores (the path it otherwise takes only when the driver refuses out's strides).
  */
 #define FMLA_OPTION_PLAIN_Q_LOADS 1
+#define FMLA_OPTION_PLAIN_STORES  2
 int fmla_set_option(int option, int value);
 
 /*

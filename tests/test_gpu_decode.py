@@ -168,6 +168,26 @@ def test_plain_load_q_path():
     assert all(torch.equal(a, b) for a, b in zip(ref, got))
 
 
+def test_plain_store_epilogue_path():
+    """Results normally leave through TMA box stores; the plain-store epilogue (taken when the driver refuses out's
+    strides for a tensor map) is forced here through fmla_set_option and must give the same bits, for unsplit and
+    split requests and for the prefill kernel."""
+    lib = _lib.load()
+    w = wl.make_decode_workload(5, 2, 128, 1024, 1100, 4000, seed=79, invalid_frac=0.05, with_sink=True, **REFD)
+    from gpu_utils import run_prefill
+    pw = wl.make_prefill_workload(150, 900, 128, 256, seed=80, std=0.1, sm_scale=0.5)
+    out0, lse0, _ = run_decode(w)
+    ref = run_prefill(pw)
+    try:
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_STORES, 1))
+        out1, lse1, _ = run_decode(w)
+        got = run_prefill(pw)
+    finally:
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_STORES, 0))
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
+    assert all(torch.equal(a, b) for a, b in zip(ref, got))
+
+
 def _raw_decode(w, kernel=None, monkeypatch=None):
     """flash_mla_with_kvcache without the helper's status assertion; returns (out, lse, status)."""
     import flashmla_b200
