@@ -10,9 +10,11 @@ Differences from the reference, all additive:
   * ``flash_mla_with_kvcache`` takes a keyword-only ``attn_done_event`` (a timing event recorded
     between its two kernels).
   * ``flash_mla_sparse_bwd`` and ``SparseMLAFunction`` provide the backward of the sparse prefill.
-  * the dense decode branch (``indices is None``) raises NotImplementedError: this package covers the
-    token-sparse path only.
-torch is used for device memory and streams only; every computation runs in the CUDA library.
+  * the dense decode branch (``indices is None``, bf16 cache with block_table / cache_seqlens / causal), for which
+    the reference has no sm_100 kernel, runs on the sparse prefill kernels over index lists that enumerate each
+    request's cache rows (see _dense_decode); an FP8 cache without indices raises NotImplementedError.
+torch is used for device memory, streams and, in the dense branch, for building those index lists (integer indexing on
+the device); every attention computation runs in the CUDA library.
 """
 from __future__ import annotations
 
@@ -113,6 +115,56 @@ def _require_cuda(t: torch.Tensor, name: str):
         raise RuntimeError(f"{name} must be a CUDA tensor; flashmla_b200 has no CPU path")
 
 
+def _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_scale, causal, is_fp8_kvcache):
+    """Dense MLA decode over a paged bf16 cache (the reference has no sm_100 kernel for it: csrc/api/dense_decode.h:27-29;
+    semantics as its torch reference, tests/test_flash_mla_dense_decoding.py:73-141).
+
+    Runs as a sparse prefill whose index lists enumerate the cache rows of each request: query row j of request i
+    becomes one "query token" per kv head with the list block_table[i][t // page] * page + t % page for the tokens t it
+    may see (all cache_seqlens[i] of them, or cache_seqlens[i] - (s_q - 1 - j) with ``causal``), and the attention
+    kernel's own per-query length does the masking.  No host synchronisation: the lists are as long as the block table
+    allows and the lengths stay on the device.
+    """
+    _require_cuda(q, "q")
+    if is_fp8_kvcache:
+        raise NotImplementedError("dense MLA decode takes a bf16 cache; FP8 caches are read through top-k indices")
+    if q.dim() != 4 or k_cache.dim() != 4 or block_table.dim() != 2 or cache_seqlens.dim() != 1:
+        raise RuntimeError("q must be (b, s_q, h_q, d), k_cache (num_blocks, page_block_size, h_kv, d), block_table (b, max_blocks), cache_seqlens (b,)")
+    b, s_q, h_q, d_qk = q.shape
+    num_blocks, page, h_kv, d_k = k_cache.shape
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise RuntimeError("dense MLA decode: q and k_cache must be bfloat16")
+    if d_qk != D_QK or d_k != D_QK or head_dim_v != D_V:
+        raise RuntimeError(f"dense MLA decode: only head_dim 576 with head_dim_v 512 is supported (got {d_qk}, {d_k}, {head_dim_v})")
+    if h_q % h_kv != 0:
+        raise RuntimeError("dense MLA decode: num_heads_q must be a multiple of num_heads_k")
+    if block_table.shape[0] != b or cache_seqlens.shape[0] != b or block_table.dtype != torch.int32 or cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("dense MLA decode: block_table must be int32 (b, max_blocks) and cache_seqlens int32 (b,)")
+    for name, t in (("k_cache", k_cache), ("block_table", block_table), ("cache_seqlens", cache_seqlens)):
+        if t.device != q.device:
+            raise RuntimeError(f"{name} must be on the same device as q")
+    if not k_cache.is_contiguous():
+        raise RuntimeError("dense MLA decode: k_cache must be contiguous")
+    dev = q.device
+    hg = h_q // h_kv
+    max_len = block_table.shape[1] * page
+    pos = torch.arange(max_len, device=dev, dtype=torch.int32)
+    rows = block_table[:, (pos // page).long()] * page + (pos % page)                 # [b, max_len] cache token of position t
+    seen = cache_seqlens.view(b, 1).expand(b, s_q)
+    if causal:
+        seen = seen - (s_q - 1 - torch.arange(s_q, device=dev, dtype=torch.int32)).view(1, s_q)
+    seen = seen.clamp(min=0)                                                           # [b, s_q] tokens visible to each row
+    heads = torch.arange(h_kv, device=dev, dtype=torch.int32)
+    idx = rows.view(b, 1, 1, max_len) * h_kv + heads.view(1, 1, h_kv, 1)               # row of (token, kv head) in the flat cache
+    idx = torch.where(pos.view(1, 1, 1, max_len) < seen.view(b, s_q, 1, 1), idx.expand(b, s_q, h_kv, max_len),
+                      torch.full((), -1, device=dev, dtype=torch.int32))
+    n = b * s_q * h_kv
+    out, _, lse = flash_mla_sparse_fwd(q.reshape(n, hg, d_qk), k_cache.view(num_blocks * page * h_kv, 1, d_k),
+                                       idx.reshape(n, 1, max_len).contiguous(), softmax_scale, head_dim_v, None,
+                                       seen.view(b, s_q, 1).expand(b, s_q, h_kv).reshape(n).contiguous())
+    return out.view(b, s_q, h_q, head_dim_v), lse.view(b, s_q, h_q).transpose(1, 2)
+
+
 def flash_mla_with_kvcache(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -134,7 +186,8 @@ def flash_mla_with_kvcache(
     kvcache_layout: Optional[str] = None,
     attn_done_event: Optional["torch.cuda.Event"] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Sparse MLA decode over a paged FP8 KV cache (flash_mla_interface.py:53-173 of the reference).
+    """Sparse MLA decode over a paged FP8 KV cache, or, with indices=None, dense MLA decode over a paged bf16 cache with
+    block_table / cache_seqlens / causal (see _dense_decode) (flash_mla_interface.py:53-173 of the reference).
 
     q: (b, s_q, h_q, 576) bf16.  k_cache: (num_blocks, page_block_size, 1, 656) bytes (fp8/uint8/int8);
     the block stride may exceed page_block_size*656.  With q (b, s_q, h_q, 512) the cache is the reference's MODEL1
@@ -178,7 +231,11 @@ def flash_mla_with_kvcache(
         assert cfg.extra_topk == extra_topk, "sched_meta.config.extra_topk must be equal to the last dim of extra_indices_in_kvcache." + msg
 
     if topk is None:
-        raise NotImplementedError("dense MLA decode (indices=None) is not part of flashmla_b200; pass top-k indices")
+        # Dense attention (flash_mla_interface.py:161-170 of the reference)
+        assert attn_sink is None and extra_k_cache is None and extra_indices_in_kvcache is None and topk_length is None and extra_topk_length is None, \
+            "indices_in_kvcache, attn_sink, extra_k_cache, extra_indices_in_kvcache, topk_length and extra_topk_length must be None when dense attention is used."
+        assert block_table is not None and cache_seqlens is not None, "block_table and cache_seqlens must be provided when dense attention is used."
+        return _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_scale, causal, is_fp8_kvcache)
     assert not causal, "causal must be False when sparse attention is enabled"
     assert is_fp8_kvcache, "is_fp8_kvcache must be True when sparse attention is enabled"
     if extra_k_cache is not None:

@@ -177,3 +177,39 @@ def sparse_prefill_bwd(
         dk.masked_fill_(invalid.unsqueeze(-1), 0.0)
         dkv.index_add_(0, idx.reshape(-1), dk.reshape(-1, d_qk))
     return dq, dkv.view(s_kv, 1, d_qk)
+
+
+def dense_decode(q: torch.Tensor, blocked_k: torch.Tensor, block_table: torch.Tensor, cache_seqlens: torch.Tensor,
+                 d_v: int = 512, causal: bool = False, sm_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dense MLA decode over a paged bf16 cache, restated from the reference's own torch reference
+    (tests/test_flash_mla_dense_decoding.py:73-141).
+
+    q [b, s_q, h_q, d] bf16, blocked_k [num_blocks, page, h_kv, d] bf16, block_table [b, max_blocks] int32,
+    cache_seqlens [b] int32.  Request i attends the first cache_seqlens[i] tokens of its blocks; with ``causal`` query
+    row j of its s_q rows sees only the first cache_seqlens[i] - (s_q - 1 - j).  Head h reads kv head h // (h_q / h_kv).
+    Returns (out [b, s_q, h_q, d_v] in q's dtype, lse [b, h_q, s_q] fp32 natural log; a row that sees nothing gives
+    out = 0 and lse = +inf).
+    """
+    b, s_q, h_q, d = q.shape
+    page, h_kv = blocked_k.shape[1], blocked_k.shape[2]
+    scale = d ** -0.5 if sm_scale is None else sm_scale
+    out = torch.zeros((b, s_q, h_q, d_v), dtype=torch.float32)
+    lse = torch.full((b, h_q, s_q), float("inf"), dtype=torch.float32)
+    for i in range(b):
+        n = int(cache_seqlens[i])
+        if n == 0:
+            continue
+        blocks = block_table[i, : (n + page - 1) // page].long()
+        kv = blocked_k[blocks].reshape(-1, h_kv, d)[:n].float()                     # [n, h_kv, d]
+        kv = kv.repeat_interleave(h_q // h_kv, dim=1)                                  # [n, h_q, d]
+        logits = torch.einsum("shd,nhd->hsn", q[i].float(), kv) * scale               # [h_q, s_q, n]
+        if causal and s_q > 1:
+            visible = torch.ones(s_q, n, dtype=torch.bool).tril(diagonal=n - s_q)
+            logits = logits.masked_fill(~visible, float("-inf"))
+        row_lse = torch.logsumexp(logits, dim=-1)                                      # [h_q, s_q]
+        dead = row_lse == float("-inf")
+        p = torch.softmax(logits, dim=-1)
+        p = torch.where(dead.unsqueeze(-1), torch.zeros_like(p), p)
+        out[i] = torch.einsum("hsn,nhv->shv", p, kv[..., :d_v])
+        lse[i] = torch.where(dead, torch.full_like(row_lse, float("inf")), row_lse)
+    return out.to(q.dtype), lse

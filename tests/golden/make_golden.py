@@ -158,6 +158,27 @@ def golden_prefill(ref_lib, ref_ref, name, *, s_q, s_kv, h_q, topk, seed, with_s
         out=bits(out), out_f32=bits(out_f32), max_logits=bits(max_logits), lse=bits(lse), **extra)
 
 
+def golden_dense(ref_root, name, *, b, s_q, h_q, h_kv, s_k, page, causal, seed, zero_len=False):
+    """Dense MLA decode: the torch reference inside the reference's own test file
+    (tests/test_flash_mla_dense_decoding.py:73-141), imported with a stand-in for its helper package."""
+    kk = types.ModuleType("kernelkit")
+    kk.cdiv = lambda a, b: (a + b - 1) // b
+    sys.modules["kernelkit"] = kk
+    import test_flash_mla_dense_decoding as ref_dense   # noqa
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(max(s_q, s_k // 3), s_k + 1, (b,), generator=g, dtype=torch.int32)
+    if zero_len:
+        lens[1] = 0
+    max_blocks = (int(lens.max()) + page - 1) // page + 1
+    block_table = torch.randperm(b * max_blocks, generator=g).to(torch.int32).view(b, max_blocks)
+    d = 576
+    q = (torch.randn((b, s_q, h_q, d), generator=g)).to(torch.bfloat16)
+    blocked_k = (torch.randn((b * max_blocks, page, h_kv, d), generator=g) / 10).to(torch.bfloat16)
+    out, lse = ref_dense.reference_torch(lens, block_table, q, blocked_k, 512, causal)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), q=bits(q), blocked_k=bits(blocked_k), block_table=block_table.numpy(),
+                        cache_seqlens=lens.numpy(), causal=np.array(causal), out=bits(out), lse=lse.numpy())
+
+
 def main():
     if len(sys.argv) < 2:
         sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
@@ -189,6 +210,9 @@ def main():
                   invalid_frac=0.03, layout=wl.LAYOUT_MODEL1, q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55)
     golden_prefill(ref_lib, ref_ref, "prefill_d512_h128", s_q=4, s_kv=300, h_q=128, topk=256, seed=13, with_sink=True,
                    with_topk_length=True, sm_scale=0.5, std=0.1, d_qk=512)
+    # dense decode (bf16 paged cache, block table, causal among the s_q rows, two kv heads, a request of length zero)
+    golden_dense(ref_root, "dense_decode", b=3, s_q=2, h_q=16, h_kv=2, s_k=200, page=64, causal=True, seed=21, zero_len=True)
+    golden_dense(ref_root, "dense_decode_h128", b=2, s_q=3, h_q=128, h_kv=1, s_k=300, page=64, causal=False, seed=22)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -90,8 +90,11 @@ def test_python_interface_refuses_cpu_tensors_and_dense_mode():
         flash_mla.flash_mla_with_kvcache(q, kc, None, None, 512, flash_mla.get_mla_metadata()[0], None, None, False, False, idx)
     with pytest.raises(AssertionError, match="causal must be False"):
         flash_mla.flash_mla_with_kvcache(q, kc, None, None, 512, flash_mla.get_mla_metadata()[0], None, None, True, True, idx)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(AssertionError, match="block_table and cache_seqlens must be provided when dense attention is used"):
         flash_mla.flash_mla_with_kvcache(q, kc, None, None, 512, flash_mla.get_mla_metadata()[0])
+    with pytest.raises(RuntimeError, match="no CPU path"):      # the dense branch has no CPU path either
+        flash_mla.flash_mla_with_kvcache(q, torch.zeros((2, 64, 1, 576), dtype=torch.bfloat16), torch.zeros((1, 2), dtype=torch.int32),
+                                         torch.ones((1,), dtype=torch.int32), 512, flash_mla.get_mla_metadata()[0])
     with pytest.raises(RuntimeError, match="no CPU path"):
         flash_mla.flash_mla_with_kvcache(q, kc, None, None, 512, flash_mla.get_mla_metadata()[0], None, None, False, True, idx)
     with pytest.raises(RuntimeError, match="no CPU path"):

@@ -1,0 +1,89 @@
+"""Dense MLA decode (indices=None: bf16 paged cache, block_table, cache_seqlens, causal) through the reference's
+flash_mla_with_kvcache signature (flash_mla_interface.py:161-170).  The reference has no sm_100 kernel for this branch
+(csrc/api/dense_decode.h:27-29); its semantics are those of the torch reference in its own test file
+(tests/test_flash_mla_dense_decoding.py:73-141), which made the fixtures."""
+import random
+
+import pytest
+import torch
+
+import flash_mla
+import flashmla_b200
+from oracle import attention
+from oracle.compare import assert_close, assert_north_out, NORTH_LSE
+from helpers import bf16, load_golden, t
+from gpu_utils import DEV, cu
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(q, blocked_k, block_table, cache_seqlens, causal, scale=None):
+    out, lse = flash_mla.flash_mla_with_kvcache(cu(q), cu(blocked_k), cu(block_table), cu(cache_seqlens), 512,
+                                                flash_mla.get_mla_metadata()[0], None, scale, causal)
+    assert flashmla_b200.kernel_status(DEV) == 0
+    return out.float().cpu(), lse.float().cpu()
+
+
+@pytest.mark.parametrize("name", ["dense_decode", "dense_decode_h128"])
+def test_golden_reference_outputs(name):
+    g = load_golden(name)
+    out, lse = _run(bf16(g["q"]), bf16(g["blocked_k"]), t(g["block_table"]), t(g["cache_seqlens"]), bool(g["causal"]))
+    assert tuple(lse.shape) == (g["q"].shape[0], g["q"].shape[2], g["q"].shape[1])
+    assert_north_out("out", out, bf16(g["out"]).float())
+    assert_close("lse", lse, t(g["lse"]), **NORTH_LSE)
+
+
+# b, s_q, h_q, h_kv, mean s_k, varlen, causal, zero-length requests  (the reference's matrix: b {1,2,6,64} x s_q {1,2,4} x
+# s_k {20,140,4096} x h_q x h_kv {1,2,3,8} x varlen x causal, and its corner case with empty caches)
+CASES = [
+    (1, 1, 128, 1, 20, False, False, False),
+    (2, 2, 128, 1, 140, True, True, False),
+    (6, 4, 64, 1, 4096, True, True, False),
+    (6, 1, 128, 2, 140, True, False, False),
+    (3, 2, 9, 3, 140, False, True, False),
+    (2, 4, 126, 2, 300, True, True, False),
+    (64, 2, 128, 1, 500, True, True, True),
+    (5, 2, 16, 8, 1000, True, False, True),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"b{c[0]}sq{c[1]}h{c[2]}hk{c[3]}sk{c[4]}{'v' if c[5] else ''}{'c' if c[6] else ''}{'z' if c[7] else ''}" for c in CASES])
+def test_against_oracle(case):
+    b, s_q, h_q, h_kv, s_k, varlen, causal, zeros = case
+    rng = random.Random(b * 1000 + s_k)
+    g = torch.Generator().manual_seed(b * 31 + s_k)
+    page, d = 64, 576
+    lens = [max(int(rng.normalvariate(s_k, s_k / 2)), s_q) if varlen else s_k for _ in range(b)]
+    if zeros:
+        for i in rng.sample(range(b), max(1, b // 4)):
+            lens[i] = 0
+    lens = torch.tensor(lens, dtype=torch.int32)
+    max_blocks = (int(lens.max()) + page - 1) // page + 1
+    block_table = torch.randperm(b * max_blocks, generator=g).to(torch.int32).view(b, max_blocks)
+    q = torch.randn((b, s_q, h_q, d), generator=g).to(torch.bfloat16)
+    blocked_k = (torch.randn((b * max_blocks, page, h_kv, d), generator=g) / 10).to(torch.bfloat16)
+    # what lies beyond a request's length must not be read: poison it like the reference's generator does
+    flat = blocked_k.view(-1, page, h_kv, d)
+    for i in range(b):
+        n = int(lens[i])
+        for j, blk in enumerate(block_table[i].tolist()):
+            lo = max(n - j * page, 0)
+            if lo < page:
+                flat[blk, lo:] = float("nan")
+    out, lse = _run(q, blocked_k, block_table, lens, causal)
+    ref_out, ref_lse = attention.dense_decode(q, torch.nan_to_num(blocked_k, nan=0.0), block_table, lens, 512, causal)
+    assert_north_out("out", out, ref_out.float())
+    assert_close("lse", lse, ref_lse, **NORTH_LSE)
+
+
+def test_the_reference_s_argument_checks():
+    q = torch.zeros((2, 1, 128, 576), dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros((4, 64, 1, 576), dtype=torch.bfloat16, device=DEV)
+    bt = torch.zeros((2, 2), dtype=torch.int32, device=DEV)
+    lens = torch.ones((2,), dtype=torch.int32, device=DEV)
+    with pytest.raises(AssertionError, match="block_table and cache_seqlens must be provided"):
+        flash_mla.flash_mla_with_kvcache(q, kc, None, lens, 512, flash_mla.get_mla_metadata()[0])
+    with pytest.raises(AssertionError, match="must be None when dense attention is used"):
+        flash_mla.flash_mla_with_kvcache(q, kc, bt, lens, 512, flash_mla.get_mla_metadata()[0], attn_sink=torch.zeros(128, device=DEV))
+    with pytest.raises(NotImplementedError):
+        flash_mla.flash_mla_with_kvcache(q, kc, bt, lens, 512, flash_mla.get_mla_metadata()[0], is_fp8_kvcache=True)

@@ -157,3 +157,38 @@ def test_backward_matches_autograd_and_finite_differences():
             return float((o * w.dout.double()).sum())
         fd = (f(eps) - f(-eps)) / (2 * eps)
         assert abs(fd - float(dkv[r, 0, c])) < 1e-5 * max(1.0, abs(fd)), (r, c, fd, float(dkv[r, 0, c]))
+
+
+@pytest.mark.parametrize("name", ["dense_decode", "dense_decode_h128"])
+def test_dense_decode_oracle_matches_the_reference(name):
+    """Dense MLA decode (bf16 paged cache, block table, causal among the s_q rows): the oracle against the torch
+    reference inside the reference's own test file (tests/test_flash_mla_dense_decoding.py:73-141)."""
+    g = load_golden(name)
+    out, lse = attention.dense_decode(bf16(g["q"]), bf16(g["blocked_k"]), t(g["block_table"]), t(g["cache_seqlens"]), 512,
+                                      bool(g["causal"]))
+    assert_close("out", out.float(), bf16(g["out"]).float(), abs_tol=2e-3, rel_tol=8e-3, cos_tol=1e-5)      # both are rounded to bf16
+    assert_close("lse", lse, t(g["lse"]), abs_tol=1e-5, rel_tol=1e-5, cos_tol=1e-6)
+
+
+def test_dense_decode_is_sparse_decode_over_every_cached_token():
+    """The product runs dense decode as a sparse prefill over index lists that enumerate the cache: the two oracles
+    must agree on that construction."""
+    g = load_golden("dense_decode")
+    q, kc, bt, lens = bf16(g["q"]), bf16(g["blocked_k"]), t(g["block_table"]), t(g["cache_seqlens"])
+    causal = bool(g["causal"])
+    b, s_q, h_q, d = q.shape
+    nb, page, h_kv, _ = kc.shape
+    hg = h_q // h_kv
+    ref_out, ref_lse = attention.dense_decode(q, kc, bt, lens, 512, causal)
+    max_len = bt.shape[1] * page
+    pos = torch.arange(max_len)
+    rows = bt[:, pos // page].long() * page + pos % page
+    flat = kc.reshape(nb * page * h_kv, 1, d)
+    for i in range(b):
+        for j in range(s_q):
+            seen = max(int(lens[i]) - (s_q - 1 - j if causal else 0), 0)
+            for k in range(h_kv):
+                idx = torch.where(pos < seen, rows[i] * h_kv + k, torch.full_like(pos, -1)).to(torch.int32).view(1, 1, max_len)
+                o, _, _, l = attention.sparse_prefill_fwd(q[i, j, k * hg:(k + 1) * hg].unsqueeze(0), flat, idx, d ** -0.5)
+                assert_close("out", o[0].float(), ref_out[i, j, k * hg:(k + 1) * hg].float(), abs_tol=2e-3, rel_tol=8e-3, cos_tol=1e-5)
+                assert_close("lse", l[0], ref_lse[i, k * hg:(k + 1) * hg, j], abs_tol=1e-5, rel_tol=1e-5, cos_tol=1e-6)
