@@ -47,8 +47,31 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("case", CASES, ids=[f"b{c[0]}sq{c[1]}h{c[2]}hk{c[3]}sk{c[4]}{'v' if c[5] else ''}{'c' if c[6] else ''}{'z' if c[7] else ''}" for c in CASES])
+def _case_id(c):
+    return f"b{c[0]}sq{c[1]}h{c[2]}hk{c[3]}sk{c[4]}{'v' if c[5] else ''}{'c' if c[6] else ''}{'z' if c[7] else ''}"
+
+
+# every 47th case of the reference's own correctness matrix and every 7th of its corner cases (caches of length zero),
+# tests/test_flash_mla_dense_decoding.py:203-222
+_MATRIX = [(b, s_q, h_q, h_kv, s_k, varlen, causal, False)
+           for b in [1, 2, 6, 64] for s_q in [1, 2, 4] for s_k in [20, 140, 4096] for h_q in [1, 3, 9, 63, 64, 126, 128]
+           for h_kv in [1, 2, 3, 8] for varlen in [False, True] for causal in [False, True] if h_q % h_kv == 0]
+_CORNER = [(128, 2, h_q, h_kv, 4096, True, causal, True) for h_q in [1, 3, 9, 63, 64, 126, 128] for h_kv in [1, 2, 3, 8]
+           for causal in [False, True] if h_q % h_kv == 0]
+REF_CASES = _MATRIX[::47] + _CORNER[::7]
+
+
+@pytest.mark.parametrize("case", REF_CASES, ids=[_case_id(c) for c in REF_CASES])
+def test_the_reference_s_case_matrix_sampled(case):
+    _check_case(case)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[_case_id(c) for c in CASES])
 def test_against_oracle(case):
+    _check_case(case)
+
+
+def _check_case(case):
     b, s_q, h_q, h_kv, s_k, varlen, causal, zeros = case
     rng = random.Random(b * 1000 + s_k)
     g = torch.Generator().manual_seed(b * 31 + s_k)
