@@ -10,7 +10,7 @@ combine kernel; the tile scheduler's output is cached after the first call, as i
 own timing, tests/kernelkit/bench.py:77-100).  Prints ONE JSON line on rank 0.
 
 On one GPU the default run also measures the other benchmark configurations for a few steps each
-(MXFP8 decode "c3", MODEL1 decode "m1", prefill forward "c4", prefill backward "c5") and reports them under "also".
+(MXFP8 decode "c3", MODEL1 decode "m1", prefill forward "c4", prefill backward "c5", dense bf16 decode "dense") and reports them under "also".
 
 Multi-GPU (launched by torch.distributed.run): every rank owns its own sequences and KV pages
 (decode) or its own query tokens (prefill); there is no collective in the data path.  The headline is
@@ -445,6 +445,44 @@ def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
                     "traffic = DRAM bytes of one launch from the ncu capture under profiles/"}
 
 
+def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
+    """Dense MLA decode (indices=None; the path the reference's own dense benchmark measures, benchmark/bench_flash_mla.py,
+    at b=128, s_q=2, causal, h_q=128, s_k=8192 for every request) timed like the other workloads: CUDA events per step,
+    L2 flush before every step.  The step is the whole call: the index lists built from the block table and the
+    attention kernel."""
+    import flash_mla
+    b, s_q, h_q, s_k, page, d = 128, 2, 128, 8192, 64, 576
+    g = torch.Generator(device=dev).manual_seed(seed)
+    nblk = s_k // page
+    block_table = torch.randperm(b * nblk, generator=g, device=dev).to(torch.int32).view(b, nblk)
+    q = torch.randn((b, s_q, h_q, d), generator=g, device=dev).to(torch.bfloat16)
+    k_cache = (torch.randn((b * nblk, page, 1, d), generator=g, device=dev) / 10).to(torch.bfloat16)
+    lens = torch.full((b,), s_k, dtype=torch.int32, device=dev)
+    meta = flash_mla.get_mla_metadata()[0]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    step = lambda: flash_mla.flash_mla_with_kvcache(q, k_cache, block_table, lens, 512, meta, None, None, True)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    ms = []
+    for i in range(steps):
+        flush.fill_(i)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(); step(); t1.record()
+        torch.cuda.synchronize()
+        ms.append(t0.elapsed_time(t1))
+    t = statistics.median(ms) / 1e3
+    # causal: row j of a request's s_q rows sees s_k - (s_q - 1 - j) tokens
+    seen = sum(s_k - (s_q - 1 - j) for j in range(s_q))
+    flops = 2.0 * b * h_q * seen * (576 + 512)
+    return {"workload": "dense_mla_decode_bf16_b128_sq2_h128_sk8192_causal", "metric": "dense_mla_decode_tflops", "value": flops / t / 1e12,
+            "unit": "TFLOP/s", "steps": steps, "ms_per_step": t * 1e3,
+            "kv_gbs": b * s_k * d * 2 / t / 1e9,
+            "roofline": {"bound": "tensor", "achieved": flops / t / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": flops / t / 1e12 / pk["bf16_tflops"], "traffic": None, "basis": pk["basis"],
+                         "kernel": "pair_attn_kernel<1,0> over index lists that enumerate the cache", "ms_per_launch": t * 1e3}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -592,6 +630,8 @@ def main():
                     rec["hbm_achieved_gbs"] = ob.alg_bytes / t / 1e9
                 also[key] = rec
                 del ob
+            torch.cuda.empty_cache()
+            also["dense"] = dense_decode_record(dev, args.seed + 11, pk)
             line["also"] = also
     if rank == 0:
         print(json.dumps(line))
