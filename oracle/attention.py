@@ -3,6 +3,8 @@
 Restates the reference's torch oracle:
   prefill forward  tests/ref.py:19-52   (``sparse_prefill_fwd``)
   decode           tests/ref.py:55-103  (``sparse_decode``)
+and, for the dense decode branch, the torch reference inside the reference's dense test
+  dense decode     tests/test_flash_mla_dense_decoding.py:73-141  (``dense_decode``)
 The backward has no counterpart in the reference (parity unpinned); it is the
 analytic gradient of ``sparse_prefill_fwd`` and is checked against autograd and
 finite differences in the tests.
