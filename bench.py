@@ -448,8 +448,8 @@ def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
 def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
     """Dense MLA decode (indices=None; the path the reference's own dense benchmark measures, benchmark/bench_flash_mla.py,
     at b=128, s_q=2, causal, h_q=128, s_k=8192 for every request) timed like the other workloads: CUDA events per step,
-    L2 flush before every step.  The step is the whole call: the index lists built from the block table and the
-    attention kernel."""
+    L2 flush before every step.  The step is the whole call: the split-KV attention kernel, which walks the block table
+    itself, and the combine kernel."""
     import flash_mla
     b, s_q, h_q, s_k, page, d = 128, 2, 128, 8192, 64, 576
     g = torch.Generator(device=dev).manual_seed(seed)
@@ -480,7 +480,7 @@ def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
             "kv_gbs": b * s_k * d * 2 / t / 1e9,
             "roofline": {"bound": "tensor", "achieved": flops / t / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": flops / t / 1e12 / pk["bf16_tflops"], "traffic": None, "basis": pk["basis"],
-                         "kernel": "pair_attn_kernel<1,0> over index lists that enumerate the cache", "ms_per_launch": t * 1e3}}
+                         "kernel": "pair_attn_kernel<0,3> + combine_kernel", "ms_per_launch": t * 1e3}}
 
 
 def main():

@@ -54,6 +54,20 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class DenseDecodeArgs(C.Structure):
+    _fields_ = [
+        ("device", C.c_int), ("b", C.c_int), ("s_q", C.c_int), ("h_q", C.c_int), ("causal", C.c_int), ("sm_scale", C.c_float),
+        ("q", C.c_void_p), ("q_stride_b", C.c_int64), ("q_stride_s", C.c_int64), ("q_stride_h", C.c_int64),
+        ("kv", C.c_void_p), ("num_blocks", C.c_int64), ("page_block_size", C.c_int64), ("kv_stride_row", C.c_int64),
+        ("block_table", C.c_void_p), ("block_table_stride", C.c_int64), ("max_blocks_per_seq", C.c_int64),
+        ("cache_seqlens", C.c_void_p),
+        ("out", C.c_void_p), ("o_stride_b", C.c_int64), ("o_stride_s", C.c_int64), ("o_stride_h", C.c_int64),
+        ("lse", C.c_void_p), ("lse_stride_b", C.c_int64), ("lse_stride_s", C.c_int64),
+        ("sched_meta", C.c_void_p), ("num_splits", C.c_void_p), ("num_sm_parts", C.c_int),
+        ("o_accum", C.c_void_p), ("lse_accum", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 class PrefillArgs(C.Structure):
     _fields_ = [
         ("device", C.c_int), ("s_q", C.c_int), ("s_kv", C.c_int), ("h_q", C.c_int), ("topk", C.c_int),
@@ -105,6 +119,7 @@ EXPORTS = {
     "fmla_sched_meta": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
     "fmla_sparse_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "fmla_sparse_decode_static_scratch": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "fmla_dense_decode": (C.c_int, [C.POINTER(DenseDecodeArgs), C.c_void_p]),
     "fmla_sparse_prefill_fwd": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
     "fmla_sparse_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), C.c_void_p]),
     "fmla_sparse_prefill_bwd_workspace": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int]),

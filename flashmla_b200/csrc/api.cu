@@ -66,7 +66,7 @@ using namespace fmla;
 
 extern "C" {
 
-int fmla_version(void) { return 131; }   // 130: fmla_set_option, fmla_tensor_map_cache_stats, FMLA_STATUS_* codes; 131: FMLA_OPTION_PLAIN_STORES, MODEL1 on the tensor cores
+int fmla_version(void) { return 132; }   // 130: fmla_set_option, fmla_tensor_map_cache_stats, FMLA_STATUS_* codes; 131: FMLA_OPTION_PLAIN_STORES, MODEL1 on the tensor cores; 132: fmla_dense_decode
 
 const char* fmla_last_error(void) { return g_error; }
 
@@ -165,6 +165,44 @@ int fmla_sparse_decode(const FmlaDecodeArgs* a, void* cuda_stream) {
   if (rc) return rc;
   if (a->attn_done_event) FMLA_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a->attn_done_event), stream));
   return launch_combine(*a, stream);
+}
+
+int fmla_dense_decode(const FmlaDenseDecodeArgs* a, void* cuda_stream) {
+  FMLA_REQUIRE(a != nullptr, FMLA_ERR_INVALID_ARG, "dense_decode: null argument struct");
+  FMLA_REQUIRE(a->b > 0 && a->s_q > 0 && a->h_q > 0, FMLA_ERR_INVALID_ARG, "dense_decode: b=%d s_q=%d h_q=%d must be positive", a->b, a->s_q, a->h_q);
+  FMLA_REQUIRE(a->q && a->kv && a->block_table && a->cache_seqlens && a->out && a->lse, FMLA_ERR_INVALID_ARG,
+               "dense_decode: q, kv, block_table, cache_seqlens, out and lse must be non-null");
+  FMLA_REQUIRE(a->sched_meta && a->num_splits && a->o_accum && a->lse_accum && a->num_sm_parts > 0, FMLA_ERR_INVALID_ARG,
+               "dense_decode: scheduler metadata and split-KV accumulators must be provided");
+  FMLA_REQUIRE(a->num_blocks > 0 && a->page_block_size > 0 && a->max_blocks_per_seq > 0, FMLA_ERR_INVALID_ARG,
+               "dense_decode: num_blocks=%lld page_block_size=%lld max_blocks_per_seq=%lld must be positive", (long long)a->num_blocks,
+               (long long)a->page_block_size, (long long)a->max_blocks_per_seq);
+  FMLA_REQUIRE(a->num_blocks * a->page_block_size <= 0x7fffffffLL && a->max_blocks_per_seq * a->page_block_size <= 0x7fffffffLL - 64, FMLA_ERR_UNSUPPORTED,
+               "dense_decode: the cache or a block table row holds more rows than an int32 index can address");
+  FMLA_REQUIRE(a->kv_stride_row >= FMLA_D_QK, FMLA_ERR_INVALID_ARG, "dense_decode: kv row stride %lld is smaller than 576", (long long)a->kv_stride_row);
+  FMLA_REQUIRE(a->block_table_stride >= a->max_blocks_per_seq, FMLA_ERR_INVALID_ARG, "dense_decode: block table stride %lld is smaller than its row length %lld",
+               (long long)a->block_table_stride, (long long)a->max_blocks_per_seq);
+  FMLA_REQUIRE(aligned16(a->kv) && a->kv_stride_row % 8 == 0, FMLA_ERR_ALIGNMENT, "dense_decode: kv base and row stride must be multiples of 16 bytes");
+  FMLA_REQUIRE(aligned16(a->q) && a->q_stride_b % 8 == 0 && a->q_stride_s % 8 == 0 && a->q_stride_h % 8 == 0,
+               FMLA_ERR_ALIGNMENT, "dense_decode: q base and strides must be multiples of 16 bytes");
+  FMLA_REQUIRE(aligned16(a->out) && a->o_stride_b % 8 == 0 && a->o_stride_s % 8 == 0 && a->o_stride_h % 8 == 0,
+               FMLA_ERR_ALIGNMENT, "dense_decode: out base and strides must be multiples of 16 bytes");
+  FMLA_REQUIRE(aligned16(a->o_accum), FMLA_ERR_ALIGNMENT, "dense_decode: o_accum must be 16-byte aligned");
+  FMLA_REQUIRE((reinterpret_cast<uintptr_t>(a->sched_meta) & 31u) == 0, FMLA_ERR_ALIGNMENT, "dense_decode: scheduler metadata must be 32-byte aligned");
+  FMLA_REQUIRE(tc_supported(a->h_q), FMLA_ERR_UNSUPPORTED, "dense_decode: the tensor-core kernel needs h_q to be a multiple of 64 (got %d)", a->h_q);
+  FMLA_REQUIRE(a->sm_scale > 0.f, FMLA_ERR_UNSUPPORTED, "dense_decode: the softmax scale must be positive (got %g)", (double)a->sm_scale);
+  DeviceInfo info;
+  if (int rc = device_info(a->device, &info)) return rc;
+  DeviceGuard guard(a->device);
+  FMLA_REQUIRE(guard.ok, FMLA_ERR_CUDA, "dense_decode: cannot switch to device %d", a->device);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (int rc = launch_tc_dense_decode(*a, stream)) return rc;
+  FmlaDecodeArgs c = {};          // what the combine kernel reads
+  c.b = a->b; c.s_q = a->s_q; c.h_q = a->h_q;
+  c.num_splits = a->num_splits; c.o_accum = a->o_accum; c.lse_accum = a->lse_accum;
+  c.out = a->out; c.o_stride_b = a->o_stride_b; c.o_stride_s = a->o_stride_s; c.o_stride_h = a->o_stride_h;
+  c.lse = a->lse; c.lse_stride_b = a->lse_stride_b; c.lse_stride_s = a->lse_stride_s;
+  return launch_combine(c, stream);
 }
 
 int fmla_sparse_prefill_fwd(const FmlaPrefillArgs* a, void* cuda_stream) {

@@ -84,6 +84,7 @@ void tc_map_cache_stats(unsigned long long* hits, unsigned long long* misses);
 int tc_decode_plan(int num_sms, int h_q, int s_q, int* num_sm_parts, int* fixed_overhead_blocks, int* block_topk);
 bool tc_decode_supported(const FmlaDecodeArgs& a);      // stride and scale preconditions of the tensor-core decode kernel
 int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream);
+int launch_tc_dense_decode(const FmlaDenseDecodeArgs& a, cudaStream_t stream);
 int launch_tc_prefill_fwd(const FmlaPrefillArgs& a, cudaStream_t stream);
 bool tc_bwd_supported(int h_q);
 int tc_bwd_groups(int h_q);             // units (groups of up to 128 heads) per query token

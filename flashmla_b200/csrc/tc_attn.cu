@@ -81,7 +81,10 @@ constexpr int GROWS = 64 / NGW;       // rows of a block fetched by one gather w
 // NGW gather warps (decode only)
 constexpr int QK_WARP = NSW + NPW, PV_WARP = QK_WARP + 2, GATHER_WARP = QK_WARP + 4;
 // decode runs all warps; prefill has no gather warps (24 / 20 warps)
-constexpr int threads_of(int mode) { return 32 * (GATHER_WARP + (mode == 0 ? NGW : 0)); }
+// FP8 decode (variants 0-2) passes its rows through the raw ring: gather warps fetch, converter warps dequantise.
+// Prefill and dense decode (variant 3) gather bf16 rows straight into the stages.
+constexpr bool raw_ring(int mode, int variant) { return mode == 0 && variant != 3; }
+constexpr int threads_of(bool raw) { return 32 * (GATHER_WARP + (raw ? NGW : 0)); }
 constexpr int NSTAGE_DECODE = 4, NSTAGE_PREFILL = 5, NRAW = 2, MAX_STAGES = 5;
 constexpr uint32_t PANEL = T * 128;                 // one 128B-swizzled [64 tokens x 64 dims] panel
 constexpr uint32_t ROPE_PANEL = 4 * PANEL;          // offset of the 64B-swizzled [64 x 32] RoPE panel in a stage
@@ -106,11 +109,11 @@ constexpr uint32_t TM_O = 0, TM_Q = 256, TM_S = 384, TM_COLS = 512;
 // CTA (80 per thread with 768 threads, 96 with 640: the most they can have), not the SM's whole file: an increase
 // beyond it never returns.
 constexpr int REGS_SOFTMAX = 128, REGS_GATHER = 40;
-constexpr int regs_launch(int mode) { return mode == 0 ? 80 : 96; }
-constexpr int regs_producer(int mode) { return mode == 0 ? 64 : 80; }
-constexpr int regs_issuer(int mode) { return mode == 0 ? 56 : 64; }
-static_assert(NSW * REGS_SOFTMAX + NPW * regs_producer(0) + 4 * regs_issuer(0) + NGW * REGS_GATHER <= (NSW + NPW + 4 + NGW) * regs_launch(0) &&
-              NSW * REGS_SOFTMAX + NPW * regs_producer(1) + 4 * regs_issuer(1) <= (NSW + NPW + 4) * regs_launch(1), "register pool");
+constexpr int regs_launch(bool raw) { return raw ? 80 : 96; }
+constexpr int regs_producer(bool raw) { return raw ? 64 : 80; }
+constexpr int regs_issuer(bool raw) { return raw ? 56 : 64; }
+static_assert(NSW * REGS_SOFTMAX + NPW * regs_producer(true) + 4 * regs_issuer(true) + NGW * REGS_GATHER <= (NSW + NPW + 4 + NGW) * regs_launch(true) &&
+              NSW * REGS_SOFTMAX + NPW * regs_producer(false) + 4 * regs_issuer(false) <= (NSW + NPW + 4) * regs_launch(false), "register pool");
 static_assert(NSW % 4 == 0 && NPW % 4 == 0 && NGW % 4 == 0, "roles fill whole warpgroups");
 constexpr float RESCALE_THRESHOLD = 6.f;   // log2 units the block maximum may exceed the reference maximum
 constexpr int RING = 8;                    // slots of the index and validity-mask rings
@@ -181,6 +184,9 @@ struct Params {
   int rows_per_block;            // decode: rows of the 656-byte-pitch view per cache block = block stride / 656
   int64_t total_rows;
   const SchedRecord* sched;
+  const int* block_table;        // dense decode: [b][block_table_stride] cache blocks of each request, in order
+  int64_t block_table_stride;
+  int causal;                    // dense decode: row sq of a request's s_q rows sees its first len - (s_q - 1 - sq) tokens
   const int* num_splits;
   int b, s_q;
   __nv_bfloat16* out;
@@ -198,12 +204,16 @@ struct Params {
 };
 // Params with the mode as a compile-time constant: `p.mode` in the device code below resolves to it, so each
 // instantiation of the kernel carries the code of one mode only.
-// VARIANT (decode): 0 = one cache of 656-byte rows, 1 = two such caches, 2 = one cache of MODEL1 blocks (d_qk = 512)
+// VARIANT (decode): 0 = one cache of 656-byte rows, 1 = two such caches, 2 = one cache of MODEL1 blocks (d_qk = 512),
+// 3 = dense decode: a bf16 cache of which every request attends all its tokens, found through its block table
 template <int MODE, int VARIANT>
 struct ParamsT : Params {
   static constexpr int mode = MODE;
   static constexpr int has_extra = VARIANT == 1;     // decode over two caches; a compile-time constant like the mode
   static constexpr int m1 = VARIANT == 2;            // MODEL1 rows: 448 e4m3 + 64 bf16, V = all 512 values
+  static constexpr int dense = VARIANT == 3;         // bf16 rows gathered straight into the stages, as in prefill
+  static constexpr int raw = raw_ring(MODE, VARIANT);      // rows pass through the raw ring and are dequantised into fp16 stages:
+                                                           // K, V, Q (NoPE) and P are then fp16, else bf16
 };
 
 struct Item {
@@ -225,8 +235,9 @@ __device__ __forceinline__ bool get_item(const P& p, const SchedRecord& rec, int
     if (rec.begin_req >= p.b || req > rec.end_req) return false;
     const int sq = blockIdx.y;
     const int blk_lo = req == rec.begin_req ? rec.begin_block : 0;
-    const int lim = p.topk_length ? __ldg(p.topk_length + req) : p.topk;
-    it.limit = lim < p.topk ? lim : p.topk;
+    int lim = p.topk_length ? __ldg(p.topk_length + req) : p.topk;
+    if (p.dense && p.causal) lim -= p.s_q - 1 - sq;          // the request's last s_q tokens are the queries themselves
+    it.limit = lim < p.topk ? (lim < 0 ? 0 : lim) : p.topk;
     int total = p.topk;
     it.main_end = 0x7fffffff; it.limit2 = 0; it.idx2 = nullptr;
     if (p.has_extra) {           // the extra slots follow the main ones from the next block boundary, as the scheduler counts them
@@ -310,7 +321,7 @@ __device__ __forceinline__ uint4 lds_16(uint32_t a) {
 }
 __device__ __forceinline__ uint32_t stage_addr(const Ctx& c, int s) { return c.base + SM_STAGE + (uint32_t)s * STAGE_BYTES; }
 template <class P>
-__device__ __forceinline__ int num_stages(const P& p) { return p.mode == 0 ? NSTAGE_DECODE : NSTAGE_PREFILL; }
+__device__ __forceinline__ int num_stages(const P& p) { return p.raw ? NSTAGE_DECODE : NSTAGE_PREFILL; }
 
 // Enumerates the blocks of all work items in order (registers only).
 struct BlockCursor {
@@ -381,7 +392,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // is the item's number in the pair's list, (c2, c3) its outer coordinates in q.  Returns false when the kernel is aborting.
 template <class P>
 __device__ __forceinline__ bool fill_q_positions(const P& p, const Ctx& c, uint32_t rank, int pwarp, int lane, int item, int c2, int c3, uint32_t& pos) {
-  const int nst = p.mode == 0 ? NSTAGE_DECODE : NSTAGE_PREFILL;
+  const int nst = num_stages(p);
   const int head0 = blockIdx.z * 128 + (int)rank * 64;
 #pragma unroll 1
   for (int k = 0; k < 2; ++k, ++pos) {
@@ -476,18 +487,26 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
   BlockCursor feed(p, rec), gat(p, rec);
   if (fsub && feed.live) feed.advance(p, rec);        // lanes 8-15 walk the odd blocks
 
+  // Dense decode has no index lists: token t of a request is row block_table[request][t / page] * page + t % page of the
+  // cache.  The ring then carries the cache block of each token, and the first token position of a block travels from
+  // the feeding lanes to the issuing lanes through a three-deep queue in registers (base0 = the pair being gathered).
+  int base0 = 0, base1 = 0, base2 = 0;
   auto feed_pair = [&](uint32_t j) {          // indices of blocks 2j, 2j+1 -> ring slots (2j + fsub) % RING; one cp.async group
+    int base = 0;
     if (lane < 2 * PROWS && feed.live) {
-      const int pos = feed.it.tok_lo + feed.n * T + PROWS * pwarp + frow;
+      base = feed.it.tok_lo + feed.n * T;
+      const int pos = base + PROWS * pwarp + frow;
       const uint32_t dst = ring + (((2 * j + fsub) % RING) * PROWS + frow) * 4;
+      const int* src = p.dense ? p.block_table + feed.it.req * p.block_table_stride + pos / p.page : feed.it.idx + pos;
       if (pos < feed.it.tok_hi && pos < feed.it.limit)
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(feed.it.idx + pos) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
       else
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0xffffffffu) : "memory");
       feed.advance(p, rec);
       if (feed.live) feed.advance(p, rec);
     }
     cp_async_commit();
+    if (p.dense) { base0 = base1; base1 = base2; base2 = base; }
   };
 
 #pragma unroll 1
@@ -504,6 +523,14 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
     if (issuer) {
       const uint4 v = lds_16(ring + (((2 * i + sub) % RING) * PROWS + 4 * q) * 4);
       id[0] = (int)v.x; id[1] = (int)v.y; id[2] = (int)v.z; id[3] = (int)v.w;
+    }
+    if (p.dense) {                  // cache block -> cache row (all lanes take part in the shuffle)
+      const int base = __shfl_sync(0xffffffffu, base0, 8 * sub) + PROWS * pwarp + 4 * q;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (id[k] >= 0) id[k] = id[k] * p.page + (base + k) % p.page;
+    }
+    if (issuer) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (id[k] < 0 || id[k] >= range) { id[k] = -1; continue; }      // the TMA unit zero-fills row -1
@@ -514,7 +541,7 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
 #pragma unroll 1
     for (int s = 0; s < 2 && gat.live; ++s, ++pos, gat.advance(p, rec)) {
       const uint32_t g = 2 * i + s;
-      if (gat.n == 0 && !fill_q_positions(p, c, rank, pwarp, lane, gat.item, gat.it.req, 0, pos)) return;
+      if (gat.n == 0 && !fill_q_positions(p, c, rank, pwarp, lane, gat.item, p.mode == 0 ? gat.it.sq : gat.it.req, p.mode == 0 ? gat.it.req : 0, pos)) return;
       const int st = pos % nst;
       const uint32_t use = pos / nst;
       const bool ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 12);
@@ -783,7 +810,7 @@ template <class P>
 __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem, uint32_t k) {
   constexpr uint32_t ALL = 0xffffffffu;
   // decode: NoPE k-steps are fp16 x fp16 (Q converted on load, K dequantised to fp16); RoPE k-steps are bf16
-  const uint32_t idesc_nope = p.mode == 0 ? idesc_16bit(128, 2 * T, 0, 0, false, false) : idesc_bf16(128, 2 * T, false, false);
+  const uint32_t idesc_nope = p.raw ? idesc_16bit(128, 2 * T, 0, 0, false, false) : idesc_bf16(128, 2 * T, false, false);
   constexpr uint32_t idesc_rope = idesc_bf16(128, 2 * T, false, false);
   // RoPE k-steps take Q from shared memory, where both lane halves of the accumulator would see the same 16 features;
   // the products of feature half 0 therefore leave lanes 64-127 untouched and those of half 1 lanes 0-63
@@ -824,7 +851,7 @@ __device__ void issue_qk(const P& p, const SchedRecord& rec, const Ctx& c, uint3
 template <class P>
 __device__ void issue_pv(const P& p, const SchedRecord& rec, const Ctx& c, uint32_t tmem) {
   constexpr uint32_t ALL = 0xffffffffu;
-  const uint32_t idesc = p.mode == 0 ? idesc_16bit(128, 256, 0, 0, false, true) : idesc_bf16(128, 256, false, true);
+  const uint32_t idesc = p.raw ? idesc_16bit(128, 256, 0, 0, false, true) : idesc_bf16(128, 256, false, true);
   const int nst = num_stages(p);
   Item it;
   uint32_t seq = 0;
@@ -929,14 +956,14 @@ __device__ __forceinline__ void load_q_to_tmem(const P& p, const Ctx& c, const I
   uint32_t r[32];
 #pragma unroll
   for (int k = 0; k < 8; ++k) { r[4 * k] = a[k].x; r[4 * k + 1] = a[k].y; r[4 * k + 2] = a[k].z; r[4 * k + 3] = a[k].w; }
-  if (p.mode == 0) {   // decode multiplies the NoPE part in fp16
+  if (p.raw) {   // decode over FP8 caches multiplies the NoPE part in fp16
 #pragma unroll
     for (int k = 0; k < 32; ++k) { qmax = absmax_bf16x2(qmax, r[k]); r[k] = bf16x2_to_f16x2(r[k]); }
   }
   tmem_st32(tmem_lane + TM_Q + 64 * g, r);
 #pragma unroll
   for (int k = 0; k < 8; ++k) { r[4 * k] = b[k].x; r[4 * k + 1] = b[k].y; r[4 * k + 2] = b[k].z; r[4 * k + 3] = b[k].w; }
-  if (p.mode == 0) {
+  if (p.raw) {
 #pragma unroll
     for (int k = 0; k < 32; ++k) { qmax = absmax_bf16x2(qmax, r[k]); r[k] = bf16x2_to_f16x2(r[k]); }
   }
@@ -959,7 +986,7 @@ __device__ __forceinline__ void copy_q_from_stage(const P& p, const Ctx& c, uint
       const uint4 t = lds_16(src + r * PANEL + swz(h, 4 * g + k));
       v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
     }
-    if (p.mode == 0) {   // decode multiplies the NoPE part in fp16
+    if (p.raw) {   // decode over FP8 caches multiplies the NoPE part in fp16
 #pragma unroll
       for (int k = 0; k < 16; ++k) { qmax = absmax_bf16x2(qmax, v[k]); v[k] = bf16x2_to_f16x2(v[k]); }
     }
@@ -1009,7 +1036,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
   const uint32_t xput = 2048u * (uint32_t)(1 - half) + xoff, xget = 2048u * (uint32_t)half + xoff;
   const uint32_t xsw = ((uint32_t)h >> 1) & 3u;
   const uint32_t pbuf = c.base + SM_P + team * P_BYTES, xbuf = c.base + SM_XCHG;
-  const uint32_t xbuf2 = p.mode == 0 ? pbuf : c.base + SM_XCHG2;
+  const uint32_t xbuf2 = p.raw ? pbuf : c.base + SM_XCHG2;
   const uint32_t max_mine = c.base + SM_MAX + 4u * (64 * slot + h), max_mate = c.base + SM_MAX + 4u * (64 * (slot ^ 1) + h);
   const uint32_t mref_mine = c.base + SM_MREF + 4u * (64 * team + h), mref_other = c.base + SM_MREF + 4u * (64 * (team ^ 1) + h);
   const uint32_t sum_base = c.base + SM_SUM + 4u * h, mtrue_base = c.base + SM_MTRUE + 4u * h;
@@ -1058,7 +1085,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       ok = ok && (seq == 0 || wait(c, DEC + (team ^ 1), (seq - 1) >> 1, 42));
       // decode: the PV product that read this team's P buffer last has completed (it did so about a block ago): the
       // buffer carries half of the exchange now and the block's probabilities later
-      if (p.mode == 0) ok = ok && (seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45));
+      if (p.raw) ok = ok && (seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45));
       if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
       tc_fence_after_sync();
       // of the block's 64 tokens this thread finishes 32 (tokens 32*half ..): it reads its own partial dot
@@ -1113,7 +1140,7 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         // every PV product issued so far must have completed.  This team's previous one first (decode has waited for it
         // at the top of the block): then the product before that one has completed too, and the parity of the other
         // team's barrier cannot be mistaken for that earlier completion
-        ok = p.mode == 0 || seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
+        ok = p.raw || seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
         ok = ok && wait(c, PV_DONE + (team ^ 1), (seq - 1) >> 1, 44);
         if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
         tc_fence_after_sync();
@@ -1140,14 +1167,14 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         const float2 a = fma2(make_float2(x[2 * j], x[2 * j + 1]), scale2, off2);
         const float2 e = make_float2(exp2f(a.x), exp2f(a.y));
         sum2[j & 1] = add2(sum2[j & 1], e);
-        pk[j] = p.mode == 0 ? pack_f16x2(e.x, e.y) : pack_bf16x2(e.x, e.y);
+        pk[j] = p.raw ? pack_f16x2(e.x, e.y) : pack_bf16x2(e.x, e.y);
       }
       l_sum += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
 
       // P rows of these 32 heads overwrite the pair's exchange data in the buffer: the pair barrier above (row maxima)
       // lies between the mate's reads of that data and these stores.  Prefill has not waited yet for the PV product that
       // read the buffer last.
-      if (p.mode != 0) {
+      if (!p.raw) {
         ok = seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
         if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
       }
@@ -1315,12 +1342,12 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     have = have_next;
   }
   if (p.out_tma && lane == 0) bulk_wait_all();   // this thread's output boxes are written before the CTA goes
-  if (p.mode == 0 && __any_sync(0xffffffffu, beyond_f16(q_absmax)) && lane == 0 && c.status) atomicCAS(c.status, 0, FMLA_STATUS_CLIPPED);
+  if (p.raw && __any_sync(0xffffffffu, beyond_f16(q_absmax)) && lane == 0 && c.status) atomicCAS(c.status, 0, FMLA_STATUS_CLIPPED);
 }
 
 // ---- kernel ------------------------------------------------------------------------------------------
 template <int MODE, int EXTRA>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(MODE), 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(raw_ring(MODE, EXTRA)), 1)
 pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Ctx c;
@@ -1376,18 +1403,18 @@ pair_attn_kernel(const __grid_constant__ ParamsT<MODE, EXTRA> p) {
     reg_inc<REGS_SOFTMAX>();
     softmax_role(p, rec, c, tmem, rank);
   } else if (warp < NSW + NPW) {
-    reg_dec<regs_producer(MODE)>();
-    if (p.mode == 0) convert_role(p, rec, c, rank);
+    reg_dec<regs_producer(raw_ring(MODE, EXTRA))>();
+    if (p.raw) convert_role(p, rec, c, rank);
     else producer_role(p, rec, c, rank);
   } else if (warp < GATHER_WARP) {
-    reg_dec<regs_issuer(MODE)>();
+    reg_dec<regs_issuer(raw_ring(MODE, EXTRA))>();
     if (rank == 0) {
       if (warp < PV_WARP) issue_qk(p, rec, c, tmem, (uint32_t)(warp - QK_WARP));
       else if (warp == PV_WARP) issue_pv(p, rec, c, tmem);
     }
   } else {
     reg_dec<REGS_GATHER>();
-    if (p.mode == 0) gather_role(p, rec, c, rank, warp - GATHER_WARP);
+    if (p.raw) gather_role(p, rec, c, rank, warp - GATHER_WARP);
   }
 
   tc_fence_before_sync();
@@ -1443,12 +1470,13 @@ static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
   static_cast<Params&>(pt) = p;
   if (g_plain_q_loads.load(std::memory_order_relaxed)) pt.q_tma = 0;
   if (g_plain_stores.load(std::memory_order_relaxed)) pt.out_tma = 0;
-  pair_attn_kernel<MODE, EXTRA><<<grid, threads_of(MODE), SMEM_BYTES, stream>>>(pt);
+  pair_attn_kernel<MODE, EXTRA><<<grid, threads_of(raw_ring(MODE, EXTRA)), SMEM_BYTES, stream>>>(pt);
   FMLA_CUDA(cudaGetLastError());
   return FMLA_OK;
 }
 static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
   if (p.mode != 0) return launch_mode<1, 0>(p, grid, stream);
+  if (p.block_table != nullptr) return launch_mode<0, 3>(p, grid, stream);
   if (p.layout == FMLA_LAYOUT_MODEL1) return launch_mode<0, 2>(p, grid, stream);
   return p.has_extra ? launch_mode<0, 1>(p, grid, stream) : launch_mode<0, 0>(p, grid, stream);
 }
@@ -1560,6 +1588,39 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
     p.extra_topk_length = a.extra_topk_length;
     p.indices2 = a.extra_indices; p.idx2_stride0 = a.extra_idx_stride_b; p.idx2_stride1 = a.extra_idx_stride_s;
   }
+  return tc::launch(p, dim3(2 * a.num_sm_parts, a.s_q, (a.h_q + 127) / 128), stream);
+}
+
+int launch_tc_dense_decode(const FmlaDenseDecodeArgs& a, cudaStream_t stream) {
+  tc::Params p = {};
+  p.mode = 0;
+  p.d_qk = D_QK;
+  p.h_q = a.h_q;
+  p.topk = (int)(a.max_blocks_per_seq * a.page_block_size);     // the longest token list a block table row can describe
+  p.scale_log2 = a.sm_scale * LOG2E;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a.q);
+  p.q_stride0 = a.q_stride_b; p.q_stride1 = a.q_stride_s; p.q_stride_h = a.q_stride_h;
+  p.q_tma = tc::make_q_map(&p.map_q, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 64, CU_TENSOR_MAP_SWIZZLE_128B, D_QK) &&
+            tc::make_q_map(&p.map_q_rope, a.q, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.q_stride_h, a.q_stride_s, a.q_stride_b, 32, CU_TENSOR_MAP_SWIZZLE_64B, D_QK);
+  p.block_table = a.block_table; p.block_table_stride = a.block_table_stride;
+  p.topk_length = a.cache_seqlens;
+  p.causal = a.causal && a.s_q > 1;
+  p.page = (int)a.page_block_size;
+  p.kv_bf16 = reinterpret_cast<const __nv_bfloat16*>(a.kv);
+  p.kv_stride_s = a.kv_stride_row;
+  p.s_kv = (int)(a.num_blocks * a.page_block_size);
+  p.sched = reinterpret_cast<const SchedRecord*>(a.sched_meta); p.num_splits = a.num_splits;
+  p.b = a.b; p.s_q = a.s_q;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
+  p.o_stride0 = a.o_stride_b; p.o_stride1 = a.o_stride_s; p.o_stride_h = a.o_stride_h;
+  p.lse = a.lse; p.lse_stride0 = a.lse_stride_b; p.lse_stride1 = a.lse_stride_s;
+  p.o_accum = a.o_accum; p.lse_accum = a.lse_accum;
+  p.status = a.status;
+  const uint64_t acc_rows = (uint64_t)(a.b + a.num_sm_parts) * (uint64_t)a.s_q;
+  p.out_tma = tc::make_out_map(&p.map_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.h_q, (uint64_t)a.s_q, (uint64_t)a.b, a.o_stride_h, a.o_stride_s, a.o_stride_b, 32) &&
+              tc::make_out_map(&p.map_acc, a.o_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.h_q, acc_rows, 1, D_V, (int64_t)a.h_q * D_V, (int64_t)(acc_rows * a.h_q) * D_V, 16);
+  if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_QK, (uint64_t)p.s_kv, (uint64_t)a.kv_stride_row * 2, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_QK, (uint64_t)p.s_kv, (uint64_t)a.kv_stride_row * 2, 32, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
   return tc::launch(p, dim3(2 * a.num_sm_parts, a.s_q, (a.h_q + 127) / 128), stream);
 }
 

@@ -115,15 +115,19 @@ def _require_cuda(t: torch.Tensor, name: str):
         raise RuntimeError(f"{name} must be a CUDA tensor; flashmla_b200 has no CPU path")
 
 
-def _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_scale, causal, is_fp8_kvcache):
+def _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_scale, causal, is_fp8_kvcache, sched_meta):
     """Dense MLA decode over a paged bf16 cache (the reference has no sm_100 kernel for it: csrc/api/dense_decode.h:27-29;
     semantics as its torch reference, tests/test_flash_mla_dense_decoding.py:73-141).
 
-    Runs as a sparse prefill whose index lists enumerate the cache rows of each request: query row j of request i
-    becomes one "query token" per kv head with the list block_table[i][t // page] * page + t % page for the tokens t it
-    may see (all cache_seqlens[i] of them, or cache_seqlens[i] - (s_q - 1 - j) with ``causal``), and the attention
-    kernel's own per-query length does the masking.  No host synchronisation: the lists are as long as the block table
-    allows and the lengths stay on the device.
+    One KV head and a head count that is a multiple of 64 (the MLA decode shapes): split-KV decode through
+    fmla_dense_decode, whose kernel walks each request's block table itself; ``sched_meta`` keeps the schedule and the
+    accumulators, as in the sparse branch.
+
+    Otherwise it runs as a sparse prefill whose index lists enumerate the cache rows of each request: query row j of
+    request i becomes one "query token" per kv head with the list block_table[i][t // page] * page + t % page for the
+    tokens t it may see (all cache_seqlens[i] of them, or cache_seqlens[i] - (s_q - 1 - j) with ``causal``), and the
+    attention kernel's own per-query length does the masking.  No host synchronisation either way: the lists are as long
+    as the block table allows and the lengths stay on the device.
     """
     _require_cuda(q, "q")
     if is_fp8_kvcache:
@@ -143,9 +147,14 @@ def _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_sc
     for name, t in (("k_cache", k_cache), ("block_table", block_table), ("cache_seqlens", cache_seqlens)):
         if t.device != q.device:
             raise RuntimeError(f"{name} must be on the same device as q")
-    if not k_cache.is_contiguous():
-        raise RuntimeError("dense MLA decode: k_cache must be contiguous")
     dev = q.device
+    if block_table.stride(-1) != 1 or not cache_seqlens.is_contiguous() or q.stride(-1) != 1:
+        raise RuntimeError("dense MLA decode: the last dimension of q and block_table must be contiguous, and cache_seqlens contiguous")
+    one_pitch = k_cache.stride(-1) == 1 and k_cache.stride(0) == page * k_cache.stride(1) and k_cache.stride(1) % 8 == 0
+    if h_kv == 1 and h_q % 64 == 0 and one_pitch and softmax_scale > 0 and _kernel_choice() != _lib.KERNEL_SIMT:
+        return _dense_decode_split_kv(q, k_cache, block_table, cache_seqlens, softmax_scale, causal, sched_meta)
+    if not k_cache.is_contiguous():
+        raise RuntimeError("dense MLA decode: k_cache must be contiguous (one KV head and h_q a multiple of 64: rows at one pitch)")
     hg = h_q // h_kv
     max_len = block_table.shape[1] * page
     pos = torch.arange(max_len, device=dev, dtype=torch.int32)
@@ -163,6 +172,45 @@ def _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_sc
                                        idx.reshape(n, 1, max_len).contiguous(), softmax_scale, head_dim_v, None,
                                        seen.view(b, s_q, 1).expand(b, s_q, h_kv).reshape(n).contiguous())
     return out.view(b, s_q, h_q, head_dim_v), lse.view(b, s_q, h_q).transpose(1, 2)
+
+
+def _dense_decode_split_kv(q, k_cache, block_table, cache_seqlens, softmax_scale, causal, sched_meta):
+    lib = _lib.load()
+    dev = q.device
+    stream = _stream(dev)
+    b, s_q, h_q, _ = q.shape
+    num_blocks, page = k_cache.shape[:2]
+    max_blocks = block_table.shape[1]
+    if sched_meta.tile_scheduler_metadata is None:
+        parts, overhead, block = C.c_int32(), C.c_int32(), C.c_int32()
+        _lib.check(lib.fmla_decode_plan(dev.index, h_q, s_q, _lib.KERNEL_TC, C.byref(parts), C.byref(overhead), C.byref(block)))
+        meta = torch.empty((parts.value, _lib.SCHED_META_INTS), dtype=torch.int32, device=dev)
+        splits = torch.empty((b + 1,), dtype=torch.int32, device=dev)
+        sa = _lib.SchedArgs(dev.index, b, max_blocks * page, block.value, overhead.value, parts.value,
+                            cache_seqlens.data_ptr(), meta.data_ptr(), splits.data_ptr(), 0, None)
+        _lib.check(lib.fmla_sched_meta(C.byref(sa), stream))
+        sched_meta.tile_scheduler_metadata = meta
+        sched_meta.num_splits = splits
+        sched_meta.kernel = _lib.KERNEL_TC
+    meta, splits = sched_meta.tile_scheduler_metadata, sched_meta.num_splits
+    parts = meta.shape[0]
+    if sched_meta.o_accum is None or sched_meta.o_accum.device != dev:
+        sched_meta.o_accum = torch.empty((b + parts, s_q, h_q, D_V), dtype=torch.float32, device=dev)
+        sched_meta.lse_accum = torch.empty((b + parts, s_q, h_q), dtype=torch.float32, device=dev)
+    out = torch.empty((b, s_q, h_q, D_V), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty((b, s_q, h_q), dtype=torch.float32, device=dev)
+    a = _lib.DenseDecodeArgs()
+    a.device, a.b, a.s_q, a.h_q, a.causal, a.sm_scale = dev.index, b, s_q, h_q, int(bool(causal)), float(softmax_scale)
+    a.q, a.q_stride_b, a.q_stride_s, a.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
+    a.kv, a.num_blocks, a.page_block_size, a.kv_stride_row = k_cache.data_ptr(), num_blocks, page, k_cache.stride(1)
+    a.block_table, a.block_table_stride, a.max_blocks_per_seq = block_table.data_ptr(), block_table.stride(0), max_blocks
+    a.cache_seqlens = cache_seqlens.data_ptr()
+    a.out, a.o_stride_b, a.o_stride_s, a.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    a.lse, a.lse_stride_b, a.lse_stride_s = lse.data_ptr(), lse.stride(0), lse.stride(1)
+    a.sched_meta, a.num_splits, a.num_sm_parts = meta.data_ptr(), splits.data_ptr(), parts
+    a.o_accum, a.lse_accum, a.status = sched_meta.o_accum.data_ptr(), sched_meta.lse_accum.data_ptr(), _status(dev).data_ptr()
+    _lib.check(lib.fmla_dense_decode(C.byref(a), stream))
+    return out, lse.transpose(1, 2)
 
 
 def flash_mla_with_kvcache(
@@ -235,7 +283,7 @@ def flash_mla_with_kvcache(
         assert attn_sink is None and extra_k_cache is None and extra_indices_in_kvcache is None and topk_length is None and extra_topk_length is None, \
             "indices_in_kvcache, attn_sink, extra_k_cache, extra_indices_in_kvcache, topk_length and extra_topk_length must be None when dense attention is used."
         assert block_table is not None and cache_seqlens is not None, "block_table and cache_seqlens must be provided when dense attention is used."
-        return _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_scale, causal, is_fp8_kvcache)
+        return _dense_decode(q, k_cache, block_table, cache_seqlens, head_dim_v, softmax_scale, causal, is_fp8_kvcache, sched_meta)
     assert not causal, "causal must be False when sparse attention is enabled"
     assert is_fp8_kvcache, "is_fp8_kvcache must be True when sparse attention is enabled"
     if extra_k_cache is not None:

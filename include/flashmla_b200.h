@@ -176,6 +176,43 @@ int fmla_sparse_decode(const FmlaDecodeArgs* args, void* cuda_stream);
 int fmla_sparse_decode_static_scratch(const FmlaDecodeArgs* args, void* cuda_stream);
 
 /*
+ * Dense decode over a paged bf16 cache with one KV head: every query attends all cache_seqlens[i] tokens of its request
+ * (with `causal`, query row j of s_q sees the first cache_seqlens[i] - (s_q - 1 - j)), found through the block table.
+ * Split-KV attention on the tensor-core kernel followed by the combine kernel, as in fmla_sparse_decode.  Replaces
+ * dense_attn_decode_interface (csrc/api/dense_decode.h:13-24; Python binding flash_mla_cuda.dense_decode_fwd), which
+ * the reference builds for sm_90a only (csrc/api/dense_decode.h:27-29), minus its allocations.  The scheduler output
+ * comes from fmla_sched_meta with topk = max_blocks_per_seq * page_block_size, topk_length = cache_seqlens and the
+ * plan of fmla_decode_plan(device, h_q, s_q, FMLA_KERNEL_TC).  h_q must be a multiple of 64.
+ * A request of length 0 (or rows that see no token) gets out = 0 and lse = +inf.
+ */
+typedef struct {
+  int device;
+  int b, s_q, h_q;
+  int causal;
+  float sm_scale;                /* > 0 */
+  const void* q;                 /* bf16 [b, s_q, h_q, 576], last dim contiguous */
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  const void* kv;                /* bf16 [num_blocks * page_block_size, 576]: the cache's rows at one pitch */
+  int64_t num_blocks, page_block_size;
+  int64_t kv_stride_row;         /* elements, multiple of 8 */
+  const int32_t* block_table;    /* [b, max_blocks_per_seq]: cache block of each page of a request */
+  int64_t block_table_stride;
+  int64_t max_blocks_per_seq;
+  const int32_t* cache_seqlens;  /* [b] */
+  void* out;                     /* bf16 [b, s_q, h_q, 512] */
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  float* lse;                    /* fp32 [b, s_q, h_q], natural log */
+  int64_t lse_stride_b, lse_stride_s;
+  const int32_t* sched_meta;     /* [num_sm_parts, 8] */
+  const int32_t* num_splits;     /* [b+1] */
+  int num_sm_parts;
+  float* o_accum;                /* fp32 [b + num_sm_parts, s_q, h_q, 512] scratch */
+  float* lse_accum;              /* fp32 [b + num_sm_parts, s_q, h_q] scratch */
+  int32_t* status;               /* optional, as in FmlaDecodeArgs */
+} FmlaDenseDecodeArgs;
+int fmla_dense_decode(const FmlaDenseDecodeArgs* args, void* cuda_stream);
+
+/*
  * Sparse prefill forward.  Replaces sparse_attn_prefill_interface (csrc/api/sparse_fwd.h:101-243;
  * Python binding flash_mla_cuda.sparse_prefill_fwd, csrc/api/api.cpp:12); outputs are passed in.
  */

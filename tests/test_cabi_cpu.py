@@ -31,13 +31,14 @@ def test_header_symbols_are_exported_and_bound():
 def test_struct_sizes_match_header_layout():
     # every struct is a sequence of naturally aligned ints, floats, pointers and int64: the ctypes
     # mirror must not be smaller than the sum of its fields and must be 8-byte aligned
-    for s in (_lib.SchedArgs, _lib.DecodeArgs, _lib.PrefillArgs, _lib.PrefillBwdArgs, _lib.KvQuantArgs, _lib.CacheIndexArgs):
+    for s in (_lib.SchedArgs, _lib.DecodeArgs, _lib.DenseDecodeArgs, _lib.PrefillArgs, _lib.PrefillBwdArgs, _lib.KvQuantArgs, _lib.CacheIndexArgs):
         assert C.sizeof(s) % 8 == 0 and C.alignment(s) == 8
 
 
 @pytest.mark.parametrize("fn,args", [
     ("fmla_sched_meta", _lib.SchedArgs),
     ("fmla_sparse_decode", _lib.DecodeArgs),
+    ("fmla_dense_decode", _lib.DenseDecodeArgs),
     ("fmla_sparse_prefill_fwd", _lib.PrefillArgs),
     ("fmla_sparse_prefill_bwd", _lib.PrefillBwdArgs),
     ("fmla_kv_quantize", _lib.KvQuantArgs),
@@ -74,6 +75,36 @@ def test_decode_rejects_null_pointers_bad_layout_and_misalignment():
     a.q_stride_h = 576
     a.kernel = _lib.KERNEL_TC          # 16 heads cannot use the tensor-core kernel
     assert lib.fmla_sparse_decode(C.byref(a), None) == _lib.ERR_UNSUPPORTED
+
+
+def test_dense_decode_rejects_null_pointers_bad_strides_and_head_counts():
+    lib = _lib.load()
+    a = _lib.DenseDecodeArgs()
+    a.b, a.s_q, a.h_q, a.sm_scale = 2, 1, 128, 0.1
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_INVALID_ARG
+    assert b"non-null" in lib.fmla_last_error()
+    for f in ("q", "kv", "block_table", "cache_seqlens", "out", "lse", "sched_meta", "num_splits", "o_accum", "lse_accum"):
+        setattr(a, f, 0x1000)
+    a.num_sm_parts, a.num_blocks, a.page_block_size, a.max_blocks_per_seq, a.block_table_stride = 4, 8, 64, 4, 4
+    a.q_stride_b, a.q_stride_s, a.q_stride_h = 128 * 576, 128 * 576, 576
+    a.o_stride_b, a.o_stride_s, a.o_stride_h = 128 * 512, 128 * 512, 512
+    a.kv_stride_row = 512
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_INVALID_ARG
+    assert b"row stride" in lib.fmla_last_error()
+    a.kv_stride_row = 580
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_ALIGNMENT
+    a.kv_stride_row = 576
+    a.block_table_stride = 3
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_INVALID_ARG
+    a.block_table_stride = 4
+    a.h_q = 96
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_UNSUPPORTED
+    assert b"multiple of 64" in lib.fmla_last_error()
+    a.h_q, a.sm_scale = 128, 0.0
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_UNSUPPORTED
+    a.sm_scale = 0.1
+    a.max_blocks_per_seq = a.block_table_stride = 1 << 26          # a block table row of 2^32 tokens
+    assert lib.fmla_dense_decode(C.byref(a), None) == _lib.ERR_UNSUPPORTED
 
 
 def test_python_interface_refuses_cpu_tensors_and_dense_mode():

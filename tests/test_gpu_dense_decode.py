@@ -99,6 +99,50 @@ def _check_case(case):
     assert_close("lse", lse, ref_lse, **NORTH_LSE)
 
 
+def _random_case(b, s_q, h_q, s_k, seed, spare_blocks=3):
+    g = torch.Generator().manual_seed(seed)
+    page, d = 64, 576
+    lens = torch.randint(max(s_k // 3, s_q), s_k + 1, (b,), generator=g).to(torch.int32)
+    max_blocks = (s_k + page - 1) // page + spare_blocks
+    block_table = torch.randperm(b * max_blocks, generator=g).to(torch.int32).view(b, max_blocks)
+    q = torch.randn((b, s_q, h_q, d), generator=g).to(torch.bfloat16)
+    blocked_k = (torch.randn((b * max_blocks, page, 1, d), generator=g) / 10).to(torch.bfloat16)
+    return q, blocked_k, block_table, lens
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_split_kv_kernel_agrees_with_the_composition_over_index_lists(causal, monkeypatch):
+    # one KV head and h_q % 64 == 0 run split-KV on the decode kernel (fmla_dense_decode); FMLA_KERNEL=simt takes the
+    # other route, a sparse prefill over enumerated rows, on the CUDA-core kernel: two independent paths to one result
+    q, blocked_k, block_table, lens = _random_case(9, 3, 128, 1500, seed=5)
+    out, lse = _run(q, blocked_k, block_table, lens, causal)
+    monkeypatch.setenv("FMLA_KERNEL", "simt")
+    out2, lse2 = _run(q, blocked_k, block_table, lens, causal)
+    assert_north_out("out", out, out2)
+    assert_close("lse", lse, lse2, **NORTH_LSE)
+
+
+def test_split_kv_kernel_with_strided_tensors_and_a_reused_schedule():
+    # q a slice of a wider tensor, the block table a slice of a wider table, cache rows at a pitch of 640 values; the
+    # second call reuses the first call's schedule and accumulators
+    q, blocked_k, block_table, lens = _random_case(4, 2, 64, 700, seed=9)
+    wide_q = torch.zeros((4, 2, 64, 640), dtype=torch.bfloat16)
+    wide_q[..., :576] = q
+    wide_k = torch.full((blocked_k.shape[0], 64, 1, 640), float("nan"), dtype=torch.bfloat16)
+    wide_k[..., :576] = blocked_k
+    wide_bt = torch.full((4, block_table.shape[1] + 5), -7, dtype=torch.int32)
+    wide_bt[:, :block_table.shape[1]] = block_table
+    meta = flash_mla.get_mla_metadata()[0]
+    ref_out, ref_lse = attention.dense_decode(q, blocked_k, block_table, lens, 512, True)
+    dq, dk, dbt, dl = cu(wide_q)[..., :576], cu(wide_k)[..., :576], cu(wide_bt)[:, :block_table.shape[1]], cu(lens)
+    for _ in range(2):
+        out, lse = flash_mla.flash_mla_with_kvcache(dq, dk, dbt, dl, 512, meta, None, None, True)
+        assert flashmla_b200.kernel_status(DEV) == 0
+        assert_north_out("out", out.float().cpu(), ref_out.float())
+        assert_close("lse", lse.float().cpu(), ref_lse, **NORTH_LSE)
+    assert meta.tile_scheduler_metadata is not None and meta.o_accum is not None
+
+
 def test_the_reference_s_argument_checks():
     q = torch.zeros((2, 1, 128, 576), dtype=torch.bfloat16, device=DEV)
     kc = torch.zeros((4, 64, 1, 576), dtype=torch.bfloat16, device=DEV)
