@@ -11,10 +11,11 @@ Differences from the reference, all additive:
     between its two kernels).
   * ``flash_mla_sparse_bwd`` and ``SparseMLAFunction`` provide the backward of the sparse prefill.
   * the dense decode branch (``indices is None``, bf16 cache with block_table / cache_seqlens / causal), for which
-    the reference has no sm_100 kernel, runs on the sparse prefill kernels over index lists that enumerate each
-    request's cache rows (see _dense_decode); an FP8 cache without indices raises NotImplementedError.
-torch is used for device memory, streams and, in the dense branch, for building those index lists (integer indexing on
-the device); every attention computation runs in the CUDA library.
+    the reference has no sm_100 kernel, runs split-KV on the decode kernel (fmla_dense_decode) for one KV head and
+    h_q % 64 == 0, else on the sparse prefill kernels over index lists that enumerate each request's cache rows (see
+    _dense_decode); an FP8 cache without indices raises NotImplementedError.
+torch is used for device memory, streams and, in that second dense route, for building the index lists (integer
+indexing on the device); every attention computation runs in the CUDA library.
 """
 from __future__ import annotations
 
