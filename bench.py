@@ -10,7 +10,8 @@ combine kernel; the tile scheduler's output is cached after the first call, as i
 own timing, tests/kernelkit/bench.py:77-100).  Prints ONE JSON line on rank 0.
 
 On one GPU the default run also measures the other benchmark configurations for a few steps each
-(MXFP8 decode "c3", MODEL1 decode "m1", prefill forward "c4", prefill backward "c5", dense bf16 decode "dense") and reports them under "also".
+(MXFP8 decode "c3", MODEL1 decode "m1", prefill forward "c4", prefill backward "c5", dense bf16 decode "dense", MODEL1 decode over
+two caches "m1x") and reports them under "also".
 
 Multi-GPU (launched by torch.distributed.run): every rank owns its own sequences and KV pages
 (decode) or its own query tokens (prefill); there is no collective in the data path.  The headline is
@@ -483,6 +484,39 @@ def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
                          "kernel": "pair_attn_kernel<0,3> + combine_kernel", "ms_per_launch": t * 1e3}}
 
 
+def model1_extra_record(dev, seed, pk, steps=6, warmup=3):
+    """MODEL1 decode over two caches at the reference's production shape for it (test_flash_mla_sparse_decoding.py:107-108,
+    "MODEL1 CONFIG2": h_q=128, s_q=2, d_qk=512, topk=128 over pages of 256 tokens + extra_topk=1024 over pages of 64,
+    16384-token sequences in both) with b=128, timed like the other workloads."""
+    import flash_mla
+    b, s_q, h_q, topk, xtopk, s_k = 128, 2, 128, 128, 1024, 16384
+    w = wl.make_decode_workload(b, s_q, h_q, topk, s_k, s_k, page=256, layout=wl.LAYOUT_MODEL1, seed=seed, device=str(dev),
+                                q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55, keep_bf16=False)
+    x = wl.make_decode_workload(b, s_q, h_q, xtopk, s_k, s_k, page=64, layout=wl.LAYOUT_MODEL1, seed=seed + 1, device=str(dev),
+                                q_std=1.0, kv_std=0.1, clamp=1.0, keep_bf16=False)
+    meta = flash_mla.get_mla_metadata()[0]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    step = lambda: flash_mla.flash_mla_with_kvcache(w.q, w.kv_rows, None, None, 512, meta, None, w.sm_scale, False, True, w.indices,
+                                                    None, x.kv_rows, x.indices, None, None, kvcache_layout=wl.LAYOUT_MODEL1)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    ms = []
+    for i in range(steps):
+        flush.fill_(i)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(); step(); t1.record()
+        torch.cuda.synchronize()
+        ms.append(t0.elapsed_time(t1))
+    t = statistics.median(ms) / 1e3
+    flops = 2.0 * b * s_q * h_q * (topk + xtopk) * (512 + 512)
+    return {"workload": "fp8_sparse_decode_model1_two_caches_b128_sq2_h128_topk128+1024", "metric": "fp8_sparse_mla_decode_tflops",
+            "value": flops / t / 1e12, "unit": "TFLOP/s", "steps": steps, "ms_per_step": t * 1e3,
+            "roofline": {"bound": "tensor", "achieved": flops / t / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": flops / t / 1e12 / pk["bf16_tflops"], "traffic": None, "basis": pk["basis"],
+                         "kernel": "pair_attn_kernel<0,4> + combine_kernel", "ms_per_launch": t * 1e3}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -632,6 +666,7 @@ def main():
                 del ob
             torch.cuda.empty_cache()
             also["dense"] = dense_decode_record(dev, args.seed + 11, pk)
+            also["m1x"] = model1_extra_record(dev, args.seed + 13, pk)
             line["also"] = also
     if rank == 0:
         print(json.dumps(line))

@@ -162,7 +162,7 @@ struct Params {
   int out_tma;                   // the two maps above are valid; else the epilogue stores with plain stores
   // decode with a second cache (extra_k_cache): its maps, geometry and index list; has_extra = 0 otherwise
   int has_extra, page2, rows_per_block2, extra_topk;
-  int64_t total_rows2;
+  int64_t total_rows2, kv_stride_block2;
   const uint8_t* kv_rows2;
   const int* indices2;
   int64_t idx2_stride0, idx2_stride1;
@@ -205,12 +205,13 @@ struct Params {
 // Params with the mode as a compile-time constant: `p.mode` in the device code below resolves to it, so each
 // instantiation of the kernel carries the code of one mode only.
 // VARIANT (decode): 0 = one cache of 656-byte rows, 1 = two such caches, 2 = one cache of MODEL1 blocks (d_qk = 512),
-// 3 = dense decode: a bf16 cache of which every request attends all its tokens, found through its block table
+// 3 = dense decode: a bf16 cache of which every request attends all its tokens, found through its block table,
+// 4 = two caches of MODEL1 blocks
 template <int MODE, int VARIANT>
 struct ParamsT : Params {
   static constexpr int mode = MODE;
-  static constexpr int has_extra = VARIANT == 1;     // decode over two caches; a compile-time constant like the mode
-  static constexpr int m1 = VARIANT == 2;            // MODEL1 rows: 448 e4m3 + 64 bf16, V = all 512 values
+  static constexpr int has_extra = VARIANT == 1 || VARIANT == 4;   // decode over two caches; a compile-time constant like the mode
+  static constexpr int m1 = VARIANT == 2 || VARIANT == 4;          // MODEL1 rows: 448 e4m3 + 64 bf16, V = all 512 values
   static constexpr int dense = VARIANT == 3;         // bf16 rows gathered straight into the stages, as in prefill
   static constexpr int raw = raw_ring(MODE, VARIANT);      // rows pass through the raw ring and are dequantised into fp16 stages:
                                                            // K, V, Q (NoPE) and P are then fp16, else bf16
@@ -616,10 +617,14 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
     scales = make_uint2(0u, 0u);
     if (blk >= total_blocks) return -1;
     const int id = (int)lds_u32(ring + ((blk % RING) * GROWS + (lane & 15)) * 4);
-    if (id < 0 || id >= p.total_rows) return -1;
-    const int b = id / p.page, off = id - b * p.page;
-    scales = ldg_nc_8(p.kv_rows + (int64_t)b * p.kv_stride_block + (int64_t)p.page * M1_DATA_BYTES + off * 8);
-    return b * p.rows_per_block + off;
+    bool extra = false;
+    if (p.has_extra) { uint32_t f; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(f) : "r"(flags + blk % RING)); extra = f != 0; }
+    if (id < 0 || id >= (extra ? p.total_rows2 : p.total_rows)) return -1;
+    const int page = extra ? p.page2 : p.page;
+    const int b = id / page, off = id - b * page;
+    const uint8_t* pool = extra ? p.kv_rows2 + (int64_t)b * p.kv_stride_block2 : p.kv_rows + (int64_t)b * p.kv_stride_block;
+    scales = ldg_nc_8(pool + (int64_t)page * M1_DATA_BYTES + off * 8);
+    return b * (extra ? p.rows_per_block2 : p.rows_per_block) + off;
   };
   uint2 m1_scales = make_uint2(0u, 0u);
   int m1_vrow = -1;
@@ -671,10 +676,10 @@ __device__ void gather_role(const P& p, const SchedRecord& rec, const Ctx& c, ui
       __syncwarp();                   // the stores above happen before the arrival below
       if (lane == 0) mbar_expect_tx(bar, GROWS * (rank == 0 ? 256u : 320u));
       if (rank == 0) {
-        if (piece == 0) tma_gather4(dst + q * 1024u, &p.map_nope, 0, rows, bar);
+        if (piece == 0) tma_gather4(dst + q * 1024u, extra ? &p.map_nope2 : &p.map_nope, 0, rows, bar);
       } else {
-        if (piece == 0) tma_gather4(dst + q * 768u, &p.map_rope, 256, rows, bar);
-        else if (piece == 1) tma_gather4(dst + M1_RAW_ROPE + q * 512u, &p.map_nope2, M1_D_NOPE, rows, bar);
+        if (piece == 0) tma_gather4(dst + q * 768u, extra ? &p.map_rope2 : &p.map_rope, 256, rows, bar);
+        else if (piece == 1) tma_gather4(dst + M1_RAW_ROPE + q * 512u, extra ? &p.map_scale2 : &p.map_scale, M1_D_NOPE, rows, bar);
       }
       m1_vrow = m1_vrow_next;
       m1_scales = m1_scales_next;
@@ -1477,7 +1482,7 @@ static int launch_mode(const Params& p, dim3 grid, cudaStream_t stream) {
 static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
   if (p.mode != 0) return launch_mode<1, 0>(p, grid, stream);
   if (p.block_table != nullptr) return launch_mode<0, 3>(p, grid, stream);
-  if (p.layout == FMLA_LAYOUT_MODEL1) return launch_mode<0, 2>(p, grid, stream);
+  if (p.layout == FMLA_LAYOUT_MODEL1) return p.has_extra ? launch_mode<0, 4>(p, grid, stream) : launch_mode<0, 2>(p, grid, stream);
   return p.has_extra ? launch_mode<0, 1>(p, grid, stream) : launch_mode<0, 0>(p, grid, stream);
 }
 
@@ -1515,9 +1520,13 @@ bool tc_decode_supported(const FmlaDecodeArgs& a) {
   auto pool_ok = [](int64_t stride, int64_t blocks, int64_t page) {
     return stride % ROW_BYTES == 0 && (uint64_t)(blocks - 1) * (uint64_t)(stride / ROW_BYTES) + (uint64_t)page <= 0x7fffffffull;
   };
-  if (a.layout == FMLA_LAYOUT_MODEL1)      // data rows at a pitch of 576 bytes; no second cache in this format's kernel variant
-    return a.sm_scale > 0.f && a.extra_kv == nullptr && a.kv_stride_block % M1_DATA_BYTES == 0 &&
-           (uint64_t)(a.num_blocks - 1) * (uint64_t)(a.kv_stride_block / M1_DATA_BYTES) + (uint64_t)a.page_block_size <= 0x7fffffffull;
+  if (a.layout == FMLA_LAYOUT_MODEL1) {    // data rows at a pitch of 576 bytes
+    auto m1_ok = [](int64_t stride, int64_t blocks, int64_t page) {
+      return stride % M1_DATA_BYTES == 0 && (uint64_t)(blocks - 1) * (uint64_t)(stride / M1_DATA_BYTES) + (uint64_t)page <= 0x7fffffffull;
+    };
+    return a.sm_scale > 0.f && m1_ok(a.kv_stride_block, a.num_blocks, a.page_block_size) &&
+           (a.extra_kv == nullptr || m1_ok(a.extra_kv_stride_block, a.extra_num_blocks, a.extra_page_block_size));
+  }
   if (!(a.sm_scale > 0.f) || !pool_ok(a.kv_stride_block, a.num_blocks, a.page_block_size)) return false;
   return a.extra_kv == nullptr || pool_ok(a.extra_kv_stride_block, a.extra_num_blocks, a.extra_page_block_size);
 }
@@ -1557,15 +1566,30 @@ int launch_tc_decode(const FmlaDecodeArgs& a, cudaStream_t stream) {
   // (the reference has the same requirement, csrc/sm100/decode/head64/kernel.cuh:911-912); tc_decode_supported() tells
   // the caller, which then takes the CUDA-core kernel.
   FMLA_REQUIRE(tc_decode_supported(a), FMLA_ERR_UNSUPPORTED,
-               "sparse_decode: the tensor-core kernel needs KV block strides that are multiples of 656 bytes (MODEL1: 576, and no "
-               "extra cache) and at most 2^31 rows per cache (got strides %lld / %lld)", (long long)a.kv_stride_block, (long long)a.extra_kv_stride_block);
+               "sparse_decode: the tensor-core kernel needs KV block strides that are multiples of 656 bytes (MODEL1: 576) "
+               "and at most 2^31 rows per cache (got strides %lld / %lld)", (long long)a.kv_stride_block, (long long)a.extra_kv_stride_block);
   if (m1) {
     p.rows_per_block = (int)(a.kv_stride_block / M1_DATA_BYTES);
     const uint64_t vrows = (uint64_t)(a.num_blocks - 1) * p.rows_per_block + a.page_block_size;
     if (int rc = tc::make_row_map(&p.map_nope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
     if (int rc = tc::make_row_map(&p.map_rope, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 192, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
-    if (int rc = tc::make_row_map(&p.map_nope2, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
-    p.map_rope2 = p.map_rope; p.map_scale = p.map_scale2 = p.map_nope;
+    if (int rc = tc::make_row_map(&p.map_scale, a.kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows, M1_DATA_BYTES, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    p.map_nope2 = p.map_nope; p.map_rope2 = p.map_rope; p.map_scale2 = p.map_scale;      // replaced below when there is an extra cache
+    if (a.extra_kv != nullptr) {
+      p.rows_per_block2 = (int)(a.extra_kv_stride_block / M1_DATA_BYTES);
+      const uint64_t vrows2 = (uint64_t)(a.extra_num_blocks - 1) * p.rows_per_block2 + a.extra_page_block_size;
+      if (int rc = tc::make_row_map(&p.map_nope2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows2, M1_DATA_BYTES, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+      if (int rc = tc::make_row_map(&p.map_rope2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows2, M1_DATA_BYTES, 192, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+      if (int rc = tc::make_row_map(&p.map_scale2, a.extra_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, M1_DATA_BYTES, vrows2, M1_DATA_BYTES, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+      p.has_extra = 1;
+      p.kv_rows2 = reinterpret_cast<const uint8_t*>(a.extra_kv);
+      p.kv_stride_block2 = a.extra_kv_stride_block;
+      p.page2 = (int)a.extra_page_block_size;
+      p.total_rows2 = a.extra_num_blocks * a.extra_page_block_size;
+      p.extra_topk = a.extra_topk;
+      p.extra_topk_length = a.extra_topk_length;
+      p.indices2 = a.extra_indices; p.idx2_stride0 = a.extra_idx_stride_b; p.idx2_stride1 = a.extra_idx_stride_s;
+    }
     return tc::launch(p, dim3(2 * a.num_sm_parts, a.s_q, (a.h_q + 127) / 128), stream);
   }
   p.rows_per_block = (int)(a.kv_stride_block / ROW_BYTES);

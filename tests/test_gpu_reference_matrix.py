@@ -173,6 +173,23 @@ def test_decode_model1_with_an_extra_cache(h_q, s_k, topk, page, xs_k, xtopk, xp
     _run_decode(w, x)
 
 
+@pytest.mark.parametrize("case", [EXTRA[0], EXTRA[7], EXTRA[-1]], ids=["first", "eighth", "last"])
+def test_decode_model1_with_an_extra_cache_runs_on_the_tensor_core_kernel(case, monkeypatch):
+    """Forced, so that a fall-back to the CUDA-core kernel would show as an error: the reference's MODEL1 configurations
+    all come with an extra cache (test_flash_mla_sparse_decoding.py:105-112)."""
+    monkeypatch.setenv("FMLA_KERNEL", "tc")
+    test_decode_model1_with_an_extra_cache(*case)
+
+
+def test_decode_model1_production_shape_with_an_extra_cache(monkeypatch):
+    """h_q = 128, s_q = 2, topk = 128 over pages of 256 tokens + 1024 extra slots over pages of 64 with their own lengths
+    (MODEL1 CONFIG2 / CONFIG4 of test_flash_mla_sparse_decoding.py:107-112), b = 74."""
+    monkeypatch.setenv("FMLA_KERNEL", "tc")
+    w = _decode_workload(512, 74, 2, 128, 4096, 128, 256, seed=21, with_len=True)
+    x = _decode_workload(512, 74, 2, 128, 4096, 1024, 64, seed=22, sink=False, with_len=True)
+    _run_decode(w, x)
+
+
 @pytest.mark.parametrize("d_qk,h_q", [(576, 128), (576, 64)])
 def test_decode_peak_shape_runs(d_qk, h_q):
     """b = 148, s_q = 2, topk = 16384 over 32768-token sequences (test_flash_mla_sparse_decoding.py:120-124): sampled
