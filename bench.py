@@ -446,13 +446,13 @@ def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
                     "traffic = DRAM bytes of one launch from the ncu capture under profiles/"}
 
 
-def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
+def dense_decode_record(dev, seed, pk, steps=4, warmup=3, b=128):
     """Dense MLA decode (indices=None; the path the reference's own dense benchmark measures, benchmark/bench_flash_mla.py,
     at b=128, s_q=2, causal, h_q=128, s_k=8192 for every request) timed like the other workloads: CUDA events per step,
     L2 flush before every step.  The step is the whole call: the split-KV attention kernel, which walks the block table
     itself, and the combine kernel."""
     import flash_mla
-    b, s_q, h_q, s_k, page, d = 128, 2, 128, 8192, 64, 576
+    s_q, h_q, s_k, page, d = 2, 128, 8192, 64, 576
     g = torch.Generator(device=dev).manual_seed(seed)
     nblk = s_k // page
     block_table = torch.randperm(b * nblk, generator=g, device=dev).to(torch.int32).view(b, nblk)
@@ -476,7 +476,7 @@ def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
     # causal: row j of a request's s_q rows sees s_k - (s_q - 1 - j) tokens
     seen = sum(s_k - (s_q - 1 - j) for j in range(s_q))
     flops = 2.0 * b * h_q * seen * (576 + 512)
-    return {"workload": "dense_mla_decode_bf16_b128_sq2_h128_sk8192_causal", "metric": "dense_mla_decode_tflops", "value": flops / t / 1e12,
+    return {"workload": f"dense_mla_decode_bf16_b{b}_sq2_h128_sk8192_causal", "metric": "dense_mla_decode_tflops", "value": flops / t / 1e12,
             "unit": "TFLOP/s", "steps": steps, "ms_per_step": t * 1e3,
             "kv_gbs": b * s_k * d * 2 / t / 1e9,
             "roofline": {"bound": "tensor", "achieved": flops / t / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
@@ -484,12 +484,12 @@ def dense_decode_record(dev, seed, pk, steps=4, warmup=3):
                          "kernel": "pair_attn_kernel<0,3> + combine_kernel", "ms_per_launch": t * 1e3}}
 
 
-def model1_extra_record(dev, seed, pk, steps=6, warmup=3):
+def model1_extra_record(dev, seed, pk, steps=6, warmup=3, b=128):
     """MODEL1 decode over two caches at the reference's production shape for it (test_flash_mla_sparse_decoding.py:107-108,
     "MODEL1 CONFIG2": h_q=128, s_q=2, d_qk=512, topk=128 over pages of 256 tokens + extra_topk=1024 over pages of 64,
     16384-token sequences in both) with b=128, timed like the other workloads."""
     import flash_mla
-    b, s_q, h_q, topk, xtopk, s_k = 128, 2, 128, 128, 1024, 16384
+    s_q, h_q, topk, xtopk, s_k = 2, 128, 128, 1024, 16384
     w = wl.make_decode_workload(b, s_q, h_q, topk, s_k, s_k, page=256, layout=wl.LAYOUT_MODEL1, seed=seed, device=str(dev),
                                 q_std=1.0, kv_std=0.1, clamp=1.0, sm_scale=512 ** -0.55, keep_bf16=False)
     x = wl.make_decode_workload(b, s_q, h_q, xtopk, s_k, s_k, page=64, layout=wl.LAYOUT_MODEL1, seed=seed + 1, device=str(dev),
@@ -510,7 +510,7 @@ def model1_extra_record(dev, seed, pk, steps=6, warmup=3):
         ms.append(t0.elapsed_time(t1))
     t = statistics.median(ms) / 1e3
     flops = 2.0 * b * s_q * h_q * (topk + xtopk) * (512 + 512)
-    return {"workload": "fp8_sparse_decode_model1_two_caches_b128_sq2_h128_topk128+1024", "metric": "fp8_sparse_mla_decode_tflops",
+    return {"workload": f"fp8_sparse_decode_model1_two_caches_b{b}_sq2_h128_topk128+1024", "metric": "fp8_sparse_mla_decode_tflops",
             "value": flops / t / 1e12, "unit": "TFLOP/s", "steps": steps, "ms_per_step": t * 1e3,
             "roofline": {"bound": "tensor", "achieved": flops / t / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": flops / t / 1e12 / pk["bf16_tflops"], "traffic": None, "basis": pk["basis"],
@@ -529,6 +529,9 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other configurations of the default run")
+    ap.add_argument("--record", choices=["dense", "m1x"], help="one GPU: run only this side record of the default line and print it "
+                    "(for profiler captures; --batch sets its request count)")
+    ap.add_argument("--batch", type=int, default=128)
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -537,6 +540,12 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, cfg, rank, world)
+        return
+    if args.record:
+        dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(dev)
+        fn = dense_decode_record if args.record == "dense" else model1_extra_record
+        print(json.dumps(fn(dev, args.seed + 11, peaks(), steps=args.steps, warmup=args.warmup, b=args.batch)))
         return
 
     import torch.distributed as dist

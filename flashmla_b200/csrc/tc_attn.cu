@@ -151,7 +151,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
 
 struct Params {
   CUtensorMap map_nope, map_rope;   // decode: byte views of the pool (256-byte NoPE box, 64-byte RoPE box); prefill: bf16 views of kv (64 / 32 dims)
-                                    // MODEL1 decode: 576-byte-pitch views with boxes of 256 (map_nope), 192 (map_rope) and 128 bytes (map_nope2)
+                                    // MODEL1 decode: 576-byte-pitch views with boxes of 256 (map_nope), 192 (map_rope) and 128 bytes (map_scale)
   CUtensorMap map_scale;            // decode: byte view of the pool with a 16-byte box (the scale field of a row)
   CUtensorMap map_nope2, map_rope2, map_scale2;   // the same for the extra cache
   CUtensorMap map_q;               // q as (576, h_q, s_q, b) / (576, h_q, queries, 1): boxes of 64 heads x 64 dims (128B swizzle)
