@@ -187,6 +187,7 @@ struct Params {
   const int* block_table;        // dense decode: [b][block_table_stride] cache blocks of each request, in order
   int64_t block_table_stride;
   int causal;                    // dense decode: row sq of a request's s_q rows sees its first len - (s_q - 1 - sq) tokens
+  int dense_blocks;              // dense decode: blocks in the cache (block-table entries outside [0, dense_blocks) are invalid slots)
   const int* num_splits;
   int b, s_q;
   __nv_bfloat16* out;
@@ -529,7 +530,7 @@ __device__ void producer_role(const P& p, const SchedRecord& rec, const Ctx& c, 
       const int base = __shfl_sync(0xffffffffu, base0, 8 * sub) + PROWS * pwarp + 4 * q;
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (id[k] >= 0) id[k] = id[k] * p.page + (base + k) % p.page;
+        id[k] = id[k] >= 0 && id[k] < p.dense_blocks ? id[k] * p.page + (base + k) % p.page : -1;   // a block the cache does not have: invalid slot
     }
     if (issuer) {
 #pragma unroll
@@ -1633,6 +1634,7 @@ int launch_tc_dense_decode(const FmlaDenseDecodeArgs& a, cudaStream_t stream) {
   p.kv_bf16 = reinterpret_cast<const __nv_bfloat16*>(a.kv);
   p.kv_stride_s = a.kv_stride_row;
   p.s_kv = (int)(a.num_blocks * a.page_block_size);
+  p.dense_blocks = (int)a.num_blocks;
   p.sched = reinterpret_cast<const SchedRecord*>(a.sched_meta); p.num_splits = a.num_splits;
   p.b = a.b; p.s_q = a.s_q;
   p.out = reinterpret_cast<__nv_bfloat16*>(a.out);

@@ -99,9 +99,9 @@ def _check_case(case):
     assert_close("lse", lse, ref_lse, **NORTH_LSE)
 
 
-def _random_case(b, s_q, h_q, s_k, seed, spare_blocks=3):
+def _random_case(b, s_q, h_q, s_k, seed, spare_blocks=3, page=64):
     g = torch.Generator().manual_seed(seed)
-    page, d = 64, 576
+    d = 576
     lens = torch.randint(max(s_k // 3, s_q), s_k + 1, (b,), generator=g).to(torch.int32)
     max_blocks = (s_k + page - 1) // page + spare_blocks
     block_table = torch.randperm(b * max_blocks, generator=g).to(torch.int32).view(b, max_blocks)
@@ -120,6 +120,37 @@ def test_split_kv_kernel_agrees_with_the_composition_over_index_lists(causal, mo
     out2, lse2 = _run(q, blocked_k, block_table, lens, causal)
     assert_north_out("out", out, out2)
     assert_close("lse", lse, lse2, **NORTH_LSE)
+
+
+@pytest.mark.parametrize("page", [16, 48, 200])
+def test_split_kv_kernel_with_other_page_sizes(page):
+    # the reference's dense decode takes pages of 64 tokens only (csrc/api/dense_decode.h:67); the block-table walk here
+    # takes any size, also sizes that neither divide nor are multiples of the kernel's 64-token blocks
+    q, blocked_k, block_table, lens = _random_case(5, 2, 128, 900, seed=page, page=page)
+    block_table[1, 2] = -1                      # a hole and an entry beyond the cache: their tokens count as invalid slots
+    block_table[3, 0] = blocked_k.shape[0] + 5
+    out, lse = _run(q, blocked_k, block_table, lens, True)
+    holes = block_table.clone()
+    holes[3, 0] = -1
+    ref_out, ref_lse = _dense_oracle_with_holes(q, blocked_k, holes, lens, True)
+    assert_north_out("out", out, ref_out.float())
+    assert_close("lse", lse, ref_lse, **NORTH_LSE)
+
+
+def _dense_oracle_with_holes(q, blocked_k, block_table, lens, causal):
+    """attention.dense_decode with the tokens of negative block-table entries left out: as sparse decode over the
+    enumerated rows, which is what the kernel's invalid slots mean."""
+    b, s_q, h_q, d = q.shape
+    page = blocked_k.shape[1]
+    max_len = block_table.shape[1] * page
+    pos = torch.arange(max_len)
+    blk = block_table[:, pos // page]
+    rows = torch.where(blk >= 0, blk * page + (pos % page), torch.full_like(blk, -1))       # [b, max_len]
+    idx = rows.view(b, 1, max_len).expand(b, s_q, max_len).clone()
+    seen = lens.view(b, 1) - ((s_q - 1 - torch.arange(s_q)).view(1, s_q) if causal else 0)
+    idx[pos.view(1, 1, max_len) >= seen.view(b, s_q, 1)] = -1
+    out, lse, _ = attention.sparse_decode(q, blocked_k, idx.to(torch.int32), d ** -0.5)
+    return out, lse
 
 
 def test_split_kv_kernel_with_strided_tensors_and_a_reused_schedule():
