@@ -183,7 +183,9 @@ int fmla_sparse_decode_static_scratch(const FmlaDecodeArgs* args, void* cuda_str
  * the reference builds for sm_90a only (csrc/api/dense_decode.h:27-29), minus its allocations.  The scheduler output
  * comes from fmla_sched_meta with topk = max_blocks_per_seq * page_block_size, topk_length = cache_seqlens and the
  * plan of fmla_decode_plan(device, h_q, s_q, FMLA_KERNEL_TC).  h_q must be a multiple of 64.
- * A request of length 0 (or rows that see no token) gets out = 0 and lse = +inf.
+ * A request of length 0 (or rows that see no token) gets out = 0 and lse = +inf.  Any page_block_size works (the
+ * reference takes 64 only, csrc/api/dense_decode.h:67); a block-table entry outside [0, num_blocks) makes its tokens
+ * invalid slots (they contribute nothing), as -1 does in an index list.
  */
 typedef struct {
   int device;

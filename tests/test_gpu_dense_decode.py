@@ -44,6 +44,9 @@ CASES = [
     (2, 4, 126, 2, 300, True, True, False),
     (64, 2, 128, 1, 500, True, True, True),
     (5, 2, 16, 8, 1000, True, False, True),
+    (1, 2, 256, 1, 20000, False, True, False),      # one request split over every partition, two head groups
+    (3, 1, 192, 1, 700, True, False, False),        # a last head group of 64
+    (2, 4, 64, 1, 3, False, True, False),           # fewer tokens than query rows see
 ]
 
 
