@@ -461,8 +461,13 @@ def roofline_record(bench: Bench, key, t_step, t_kernel, pk):
                                   "achieved_gbs": red_bytes / t_kernel / 1e9,
                                   "note": "fp32 red.global.add traffic of the first pass's dQ / dKV launch (592 query tokens x topk x 576 x 4 B) over its CUDA-event time"},
                 "note": "the whole step (all launches), 2*h_q*topk*(3*576+2*512) flops per query token"}
+    # the captured traffic belongs to the workload's full unit count; a part of it (a strong-scaling shard) moves in proportion
+    full = bench.cfg.get("b", bench.cfg.get("s_q"))
+    traffic = NCU_TRAFFIC.get(key)
+    if traffic is not None and bench.units != full:
+        traffic = traffic * bench.units / full
     return {"bound": "tensor", "achieved": bench.flops / t_kernel / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-            "frac": bench.flops / t_kernel / 1e12 / pk["bf16_tflops"], "traffic": NCU_TRAFFIC.get(key), "basis": pk["basis"],
+            "frac": bench.flops / t_kernel / 1e12 / pk["bf16_tflops"], "traffic": traffic, "basis": pk["basis"],
             "kernel": "pair_attn_kernel<0,2>" if key in ("m1", "m1s") else KERNEL_NAME[bench.kind], "ms_per_launch": t_kernel * 1e3,
             "note": "the attention kernel alone (one launch per step), 2*h_q*topk*(d_qk+512) flops per query token; "
                     "traffic = DRAM bytes of one launch from the ncu capture under profiles/"}
