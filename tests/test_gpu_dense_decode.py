@@ -177,6 +177,23 @@ def test_split_kv_kernel_with_strided_tensors_and_a_reused_schedule():
     assert meta.tile_scheduler_metadata is not None and meta.o_accum is not None
 
 
+def test_split_kv_kernel_with_plain_q_loads_and_plain_stores():
+    # the paths the kernel takes when the driver refuses q's or out's strides for a tensor map, forced through
+    # fmla_set_option: the same bits as with TMA tiles, for split and unsplit requests
+    from flashmla_b200 import _lib
+    lib = _lib.load()
+    q, blocked_k, block_table, lens = _random_case(40, 2, 128, 600, seed=13)
+    out0, lse0 = _run(q, blocked_k, block_table, lens, True)
+    try:
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_Q_LOADS, 1))
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_STORES, 1))
+        out1, lse1 = _run(q, blocked_k, block_table, lens, True)
+    finally:
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_Q_LOADS, 0))
+        _lib.check(lib.fmla_set_option(_lib.OPTION_PLAIN_STORES, 0))
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
+
+
 def test_the_reference_s_argument_checks():
     q = torch.zeros((2, 1, 128, 576), dtype=torch.bfloat16, device=DEV)
     kc = torch.zeros((4, 64, 1, 576), dtype=torch.bfloat16, device=DEV)
