@@ -718,6 +718,11 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     return (uint32_t)lane & 15u;
   };
   auto m1_bf16 = [&](int it) { return m1_split && it == 3; };
+  // A piece becomes two 16-byte chunks of a stage row, stored by two instructions.  The eight lanes that a 16-byte store
+  // instruction serves per cycle hold the pieces of two panels at the same four chunk positions, so if every lane
+  // stored its lower chunk first they would hit four of the eight bank groups twice; the lanes of the odd panels
+  // therefore store their upper chunk first (they swap the halves of their input and the two chunk positions).
+  const uint32_t flip = m1_split ? 0u : ((uint32_t)lane >> 2) & 1u;
   uint32_t total_blocks = 0;
   {
     Item it;
@@ -780,7 +785,8 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       }
       const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(sc_bits[it]) : e8m0_to_float(sc_bits[it]);
       clipped |= scale > MAX_STAGED_SCALE;
-      dequant_chunk_f16(in[it], scale_to_half2(scale), lo[it], hi[it]);
+      const uint4 src = flip ? make_uint4(in[it].z, in[it].w, in[it].x, in[it].y) : in[it];
+      dequant_chunk_f16(src, scale_to_half2(scale), lo[it], hi[it]);
     }
     // only the stores need the stage: everything above overlaps the products that still read its previous contents
     const uint32_t use = pos / NSTAGE_DECODE;
@@ -790,8 +796,9 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     for (int it = 0; it < PROWS / 2; ++it) {
       const uint32_t row = piece_row(it), ch = piece_ch(it);
       const uint32_t panel = stage + (ch >> 2) * PANEL;
-      st_shared16(panel + swz(row, 2 * (ch & 3)), lo[it]);
-      st_shared16(panel + swz(row, 2 * (ch & 3) + 1), hi[it]);
+      const uint32_t f = m1_bf16(it) ? 0u : flip;
+      st_shared16(panel + swz(row, 2 * (ch & 3) + f), lo[it]);
+      st_shared16(panel + swz(row, 2 * (ch & 3) + 1 - f), hi[it]);
     }
     if (!p.m1) st_shared16(stage + ROPE_PANEL + rrow * 64u + ((chr ^ ((rrow >> 1) & 3u)) << 4), rope);
     // the dequantised rows (generic proxy) become visible to the MMAs, and this warp's reads of the raw slot
