@@ -770,8 +770,7 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
     uint4 rope = make_uint4(0u, 0u, 0u, 0u);
     if (!p.m1) rope = lds_16(raw + RAW_ROPE + (rrow >> 2) * ROPE_GROUP + (rrow & 3u) * 64u + chr * 16u);
     uint4 lo[PROWS / 2], hi[PROWS / 2];
-#pragma unroll
-    for (int it = 0; it < PROWS / 2; ++it) {
+    auto convert_piece = [&](int it) {
       if (m1_bf16(it)) {      // bf16 -> fp16: values beyond fp16's range saturate and are reported
         uint32_t amax = 0;
         const uint32_t w[8] = {in[it].x, in[it].y, in[it].z, in[it].w, in2[it].x, in2[it].y, in2[it].z, in2[it].w};
@@ -781,25 +780,33 @@ __device__ void convert_role(const P& p, const SchedRecord& rec, const Ctx& c, u
         clipped |= beyond_f16(amax);
         lo[it] = make_uint4(o[0], o[1], o[2], o[3]);
         hi[it] = make_uint4(o[4], o[5], o[6], o[7]);
-        continue;
+        return;
       }
       const float scale = p.layout == FMLA_LAYOUT_V32 ? __uint_as_float(sc_bits[it]) : e8m0_to_float(sc_bits[it]);
       clipped |= scale > MAX_STAGED_SCALE;
       const uint4 src = flip ? make_uint4(in[it].z, in[it].w, in[it].x, in[it].y) : in[it];
       dequant_chunk_f16(src, scale_to_half2(scale), lo[it], hi[it]);
-    }
-    // only the stores need the stage: everything above overlaps the products that still read its previous contents
-    const uint32_t use = pos / NSTAGE_DECODE;
-    ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
-    if (!__all_sync(0xffffffffu, ok)) return;
-#pragma unroll
-    for (int it = 0; it < PROWS / 2; ++it) {
+    };
+    auto store_piece = [&](int it) {
       const uint32_t row = piece_row(it), ch = piece_ch(it);
       const uint32_t panel = stage + (ch >> 2) * PANEL;
       const uint32_t f = m1_bf16(it) ? 0u : flip;
       st_shared16(panel + swz(row, 2 * (ch & 3) + f), lo[it]);
       st_shared16(panel + swz(row, 2 * (ch & 3) + 1 - f), hi[it]);
-    }
+    };
+    // Two halves: the stores of the first two pieces are under way while the last two are converted.  Only the stores
+    // need the stage: what comes before them overlaps the products that still read its previous contents.
+    convert_piece(0);
+    convert_piece(1);
+    const uint32_t use = pos / NSTAGE_DECODE;
+    ok = use == 0 || wait(c, KV_EMPTY + st, use - 1, 15);
+    if (!__all_sync(0xffffffffu, ok)) return;
+    store_piece(0);
+    store_piece(1);
+    convert_piece(2);
+    convert_piece(3);
+    store_piece(2);
+    store_piece(3);
     if (!p.m1) st_shared16(stage + ROPE_PANEL + rrow * 64u + ((chr ^ ((rrow >> 1) & 3u)) << 4), rope);
     // the dequantised rows (generic proxy) become visible to the MMAs, and this warp's reads of the raw slot
     // are ordered before the TMA writes of the slot's next use
