@@ -1182,25 +1182,24 @@ __device__ void softmax_role(const P& p, const SchedRecord& rec, const Ctx& c, u
       uint32_t pk[16];
       float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), off2 = make_float2(off, off);
+      // P rows of these 32 heads overwrite the pair's exchange data in the buffer: the pair barrier above (row maxima)
+      // lies between the mate's reads of that data and these stores.  Prefill has not waited yet for the PV product that
+      // read the buffer last.  Each 16-byte chunk is stored as soon as its eight probabilities exist, so that the stores
+      // travel under the remaining exponentials.
+      if (!p.raw) {
+        ok = seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
+        if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float2 a = fma2(make_float2(x[2 * j], x[2 * j + 1]), scale2, off2);
         const float2 e = make_float2(exp2f(a.x), exp2f(a.y));
         sum2[j & 1] = add2(sum2[j & 1], e);
         pk[j] = p.raw ? pack_f16x2(e.x, e.y) : pack_bf16x2(e.x, e.y);
+        if ((j & 3) == 3) st_shared16(pbuf + swz(h, 4 * half + (j >> 2)), make_uint4(pk[j - 3], pk[j - 2], pk[j - 1], pk[j]));
       }
       l_sum += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
 
-      // P rows of these 32 heads overwrite the pair's exchange data in the buffer: the pair barrier above (row maxima)
-      // lies between the mate's reads of that data and these stores.  Prefill has not waited yet for the PV product that
-      // read the buffer last.
-      if (!p.raw) {
-        ok = seq < 2 || wait(c, PV_DONE + team, (seq >> 1) - 1, 45);
-        if (!__all_sync(0xffffffffu, ok)) { leave_group(leave_word, warp); return; }
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        st_shared16(pbuf + swz(h, 4 * half + k), make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]));
       fence_async_smem();
       tc_fence_before_sync();
       __syncwarp();
