@@ -1,8 +1,8 @@
 """Host-side sharding of the sparse MLA path over the GPUs of one node.
 
 Decode is partitioned by batch: a rank owns a contiguous slice of the requests together with the KV
-pages those requests reference, renumbered into a rank-local pool.  Prefill is partitioned by query
-token; the bf16 KV is replicated.  There is no collective inside the kernels; results are simply
+pages those requests reference, renumbered into a rank-local pool (sparse decode: through the index lists; dense
+decode: through the block table).  Prefill is partitioned by query token; the bf16 KV is replicated.  There is no collective inside the kernels; results are simply
 concatenated in rank order.
 """
 from __future__ import annotations
@@ -41,6 +41,28 @@ def shard_decode_inputs(q: torch.Tensor, kv_rows: torch.Tensor, indices: torch.T
     local = remap[safe // page] * page + safe % page
     local = torch.where(valid, local, torch.full_like(local, -1)).to(torch.int32)
     return q[lo:hi], kv_rows[pages.long()].contiguous(), local, (lo, hi)
+
+
+def shard_dense_decode_inputs(q: torch.Tensor, k_cache: torch.Tensor, block_table: torch.Tensor, cache_seqlens: torch.Tensor,
+                              world: int, rank: int):
+    """Slice of a dense decode problem owned by `rank`.
+
+    q (b, s_q, h_q, 576), k_cache (num_blocks, page, h_kv, 576) bf16, block_table (b, max_blocks) int32,
+    cache_seqlens (b,) int32.  Returns (q_local, cache_local, block_table_local, cache_seqlens_local, (lo, hi)):
+    cache_local holds only the blocks that the slice's requests reach within their lengths, and the local block
+    table addresses it; entries beyond a request's length (never read) become 0.
+    """
+    lo, hi = shard_bounds(q.shape[0], world, rank)
+    page = k_cache.shape[1]
+    bt, lens = block_table[lo:hi], cache_seqlens[lo:hi]
+    used = torch.arange(bt.shape[1], device=bt.device).view(1, -1) * page < lens.view(-1, 1)      # pages a request reaches
+    blocks = torch.unique(bt[used])
+    if blocks.numel() == 0:
+        blocks = torch.zeros(1, dtype=bt.dtype, device=bt.device)
+    remap = torch.zeros((k_cache.shape[0],), dtype=torch.int64, device=bt.device)
+    remap[blocks.long()] = torch.arange(blocks.numel(), device=bt.device)
+    local = torch.where(used, remap[bt.clamp(0, k_cache.shape[0] - 1).long()], torch.zeros_like(bt, dtype=torch.int64)).to(torch.int32)
+    return q[lo:hi], k_cache[blocks.long()].contiguous(), local, lens, (lo, hi)
 
 
 def shard_prefill_inputs(q: torch.Tensor, indices: torch.Tensor, world: int, rank: int):

@@ -1,5 +1,5 @@
-"""The multi-GPU path on the CPU: two gloo ranks shard a decode problem by batch (each with its own
-renumbered page pool) and a prefill problem by query token, run the oracle on their shard, and the
+"""The multi-GPU path on the CPU: two gloo ranks shard a sparse and a dense decode problem by batch (each with its
+own renumbered page pool) and a prefill problem by query token, run the oracle on their shard, and the
 gathered result must equal the unsharded one bit for bit.  Also checks the max-over-ranks timing reduction
 the benchmark uses."""
 import os
@@ -36,12 +36,28 @@ def _worker(rank, world, port, out_dir):
     pout = attention.sparse_prefill_fwd(pq, p.kv, pidx, p.sm_scale)[0]
     pg = [None] * world
     dist.all_gather_object(pg, (plo, phi, pout))
+    dq, dk, dbt, dlens = _dense_problem()
+    sq, sk, sbt, slens, (dlo, dhi) = sharding.shard_dense_decode_inputs(dq, dk, dbt, dlens, world, rank)
+    assert sk.shape[0] < dk.shape[0]
+    dout, dlse = attention.dense_decode(sq, sk, sbt, slens, 512, True)
+    dg = [None] * world
+    dist.all_gather_object(dg, (dlo, dhi, dout, dlse.contiguous()))
     t = torch.tensor([1.0 + rank], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
-        torch.save({"decode": gathered, "prefill": pg, "tmax": float(t)}, os.path.join(out_dir, "r.pt"))
+        torch.save({"decode": gathered, "prefill": pg, "dense": dg, "tmax": float(t)}, os.path.join(out_dir, "r.pt"))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _dense_problem():
+    g = torch.Generator().manual_seed(11)
+    b, s_q, h_q, page, max_blocks = 5, 2, 8, 64, 6
+    lens = torch.tensor([300, 0, 64, 381, 130], dtype=torch.int32)
+    block_table = torch.randperm(b * max_blocks, generator=g).to(torch.int32).view(b, max_blocks)
+    q = torch.randn((b, s_q, h_q, 576), generator=g).to(torch.bfloat16)
+    k = (torch.randn((b * max_blocks, page, 1, 576), generator=g) / 10).to(torch.bfloat16)
+    return q, k, block_table, lens
 
 
 def test_two_rank_sharding_reproduces_unsharded_results(tmp_path):
@@ -59,6 +75,11 @@ def test_two_rank_sharding_reproduces_unsharded_results(tmp_path):
     pref = attention.sparse_prefill_fwd(p.q, p.kv, p.indices, p.sm_scale)[0]
     pp = sorted(r["prefill"], key=lambda x: x[0])
     assert torch.equal(torch.cat([x[2] for x in pp]), pref)
+    dq, dk, dbt, dlens = _dense_problem()
+    dref_out, dref_lse = attention.dense_decode(dq, dk, dbt, dlens, 512, True)
+    dd = sorted(r["dense"], key=lambda x: x[0])
+    assert torch.equal(torch.cat([x[2] for x in dd]), dref_out)
+    assert torch.equal(torch.cat([x[3] for x in dd]), dref_lse.contiguous())
 
 
 @pytest.mark.parametrize("n,world", [(128, 8), (7, 2), (3, 4), (0, 2)])
