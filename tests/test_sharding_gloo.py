@@ -89,3 +89,22 @@ def test_shard_bounds_cover(n, world):
     assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
     sizes = [hi - lo for lo, hi in spans]
     assert max(sizes) - min(sizes) <= 1
+
+
+def test_dense_shard_of_empty_requests_and_more_ranks_than_requests():
+    q, k, bt, lens = _dense_problem()
+    zero = torch.zeros_like(lens)
+    sq, sk, sbt, slens, (lo, hi) = sharding.shard_dense_decode_inputs(q, k, bt, zero, 2, 0)
+    assert (lo, hi) == (0, 3) and sk.shape[0] == 1 and int(sbt.abs().sum()) == 0          # no page reached: one stand-in block
+    out, lse = attention.dense_decode(sq, sk, sbt, slens, 512, False)
+    assert float(out.float().abs().sum()) == 0.0 and bool(torch.isinf(lse).all())
+    spans = []
+    for r in range(8):                                                                     # 8 ranks, 5 requests
+        sq, sk, sbt, slens, (lo, hi) = sharding.shard_dense_decode_inputs(q, k, bt, lens, 8, r)
+        spans.append((lo, hi))
+        assert sq.shape[0] == hi - lo == sbt.shape[0] == slens.shape[0]
+        if hi > lo:
+            ref = attention.dense_decode(q[lo:hi], k, bt[lo:hi], lens[lo:hi], 512, True)
+            got = attention.dense_decode(sq, sk, sbt, slens, 512, True)
+            assert torch.equal(ref[0], got[0]) and torch.equal(ref[1], got[1])
+    assert spans[0][0] == 0 and spans[-1][1] == 5 and sum(hi - lo for lo, hi in spans) == 5
